@@ -1,0 +1,239 @@
+/*
+ * grmx.h -- C ABI of the B200 (sm_100a) engine for GRM's segment-memory path.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues work on
+ * the CUDA stream it is given and returns immediately: no allocation, no host
+ * synchronisation, no exception crosses this boundary.  A return value of 0
+ * means "enqueued"; any other value is an argument or launch error whose text
+ * is available from grmx_last_error() on the calling thread.
+ *
+ * Tensors are dense and row-major unless a stride argument says otherwise.
+ * Shapes use the reference's names: B = op batch (batch x heads when heads
+ * are independent), T = tokens in the call, K = memory key dim (d_k),
+ * H = hidden / value dim (d_v), S = archived segments, R = routes (top-k),
+ * Q = queries per batch row.  The recurrent state is M[B, H, K], K fastest
+ * (reference: grm/csrc/grm_cuda.cpp:18-26).
+ *
+ * The file:line citations name the reference interface each call replaces
+ * (paths relative to the Sggggt/RNN_with_GRM project root).
+ */
+#ifndef GRMX_H_
+#define GRMX_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of tensors crossing the ABI */
+#define GRMX_F32 0
+#define GRMX_BF16 1
+#define GRMX_F16 2
+
+/* status codes */
+#define GRMX_OK 0
+#define GRMX_ERR_ARG 1         /* bad shape / null pointer / bad enum           */
+#define GRMX_ERR_UNSUPPORTED 2 /* valid request this build has no kernel for    */
+#define GRMX_ERR_LAUNCH 3      /* CUDA reported an error at launch              */
+#define GRMX_ERR_DEVICE 4      /* wrong device (not sm_100) for the chosen path */
+
+/* kernel family for the chunk scan */
+#define GRMX_PATH_AUTO 0    /* tcgen05 path when shape/dtype allow it, else FFMA */
+#define GRMX_PATH_FFMA 1    /* fp32 CUDA-core scan: exact mode, any shape        */
+#define GRMX_PATH_TCGEN05 2 /* bf16 tensor-core chunked scan, fp32 state         */
+
+/* fusion rule applied by grmx_retrieve_fuse */
+#define GRMX_FUSE_RETRIEVED 0 /* out[B,Q,R,H]  = M[idx] q                           */
+#define GRMX_FUSE_CONTRIB 1   /* out[B,Q,H]    = sum_r gate_r M[idx_r] q            */
+#define GRMX_FUSE_RESIDUAL_LN 2 /* out[B,Q,H]  = LayerNorm(h + sum_r gate_r M[idx_r] q) */
+
+typedef struct grmx_device_info {
+  int32_t device;
+  int32_t cc_major;
+  int32_t cc_minor;
+  int32_t sm_count;
+  int32_t max_smem_per_block; /* opt-in bytes */
+  int32_t has_tcgen05;        /* 1 when cc is 10.x */
+  int64_t total_mem;
+} grmx_device_info;
+
+/* library version: major*10000 + minor*100 + patch */
+int grmx_version(void);
+
+/* Text of the last error raised on the calling thread ("" when none). */
+const char* grmx_last_error(void);
+
+/* Fills *out for CUDA device `device`.  Host-only query (cudaGetDeviceProperties). */
+int grmx_query_device(int device, grmx_device_info* out);
+
+/* Number of kernel launches this library has enqueued in this process
+ * (all threads).  Used by the benchmark to count launches in a timed region. */
+int64_t grmx_launch_count(void);
+
+/*
+ * Chunked linear-memory update + query application.
+ *
+ *   M_t = decay * M_{t-1} + (1-decay)/sqrt(K) * v_t k_t^T      (M_{-1} = memory_in)
+ *   hidden_t = M_t q_t                                          (update is inclusive)
+ *   memory_out = M_{T-1}
+ *
+ * keys, queries [B,T,K]; values, hidden_out [B,T,H] in io_dtype; memory_in,
+ * memory_out [B,H,K] in state_dtype (GRMX_F32, or equal to io_dtype).
+ * T == 0 copies memory_in to memory_out and writes no hidden.
+ * path selects the kernel family (GRMX_PATH_*).
+ *
+ * Replaces grm_cuda::chunk_update_forward (grm/csrc/bindings.cpp:6,
+ * grm/csrc/chunk_update.cu:523-586; math grm/core/cuda_ops.py:218-254,
+ * sequential form grm/csrc/grm_cuda.cpp:46-90).
+ */
+int grmx_chunk_scan_fwd(const void* keys, const void* values, const void* queries,
+                        const void* memory_in, void* hidden_out, void* memory_out,
+                        int64_t B, int64_t T, int64_t K, int64_t H, float decay,
+                        int io_dtype, int state_dtype, int path, void* stream);
+
+/*
+ * Gradients of grmx_chunk_scan_fwd: given grad_hidden [B,T,H] (io_dtype) and
+ * grad_memory_out [B,H,K] (state_dtype) writes grad_keys, grad_queries
+ * [B,T,K], grad_values [B,T,H] (io_dtype) and grad_memory [B,H,K]
+ * (state_dtype).  Runs three scans of the forward kernel family with the
+ * operands permuted; needs no scratch memory and no saved per-token states.
+ *
+ * Replaces grm_cuda::chunk_update_backward (grm/csrc/bindings.cpp:7,
+ * grm/csrc/chunk_update.cu:588-716, grm/csrc/grm_cuda.cpp:92-126).
+ */
+int grmx_chunk_scan_bwd(const void* grad_hidden, const void* grad_memory_out,
+                        const void* keys, const void* values, const void* queries,
+                        const void* memory_in, void* grad_keys, void* grad_values,
+                        void* grad_queries, void* grad_memory, int64_t B, int64_t T,
+                        int64_t K, int64_t H, float decay, int io_dtype, int state_dtype,
+                        int path, void* stream);
+
+/*
+ * The general recurrence both calls above are built from:
+ *
+ *   M_t = a_t * M_{t-1} + update_coeff * v_t k_t^T,   hidden_t = hidden_scale * M_t q_t
+ *   a_t = decay, except a_first = 1 when first_step_no_decay != 0
+ *   memory_out = memory_out_scale * M_last
+ *
+ * Tokens are visited in increasing order, or decreasing when reverse != 0.
+ * memory_in is read with element strides (m_row_stride along H, m_col_stride
+ * along K; batch stride H*K), so a transposed state can be consumed in place.
+ * memory_out may be NULL.  No counterpart in the reference: its backward
+ * kernel (grm/csrc/chunk_update.cu:137-278) is a separate code path.
+ */
+int grmx_linear_scan(const void* keys, const void* values, const void* queries,
+                     const void* memory_in, int64_t m_row_stride, int64_t m_col_stride,
+                     void* hidden_out, void* memory_out, int64_t B, int64_t T, int64_t K,
+                     int64_t H, float decay, float update_coeff, float hidden_scale,
+                     float memory_out_scale, int reverse, int first_step_no_decay,
+                     int io_dtype, int state_dtype, int path, void* stream);
+
+/*
+ * hidden[n,r,h] = sum_k memories[n,r,h,k] * queries[n,k]
+ * memories [N,R,H,K], queries [N,K], hidden [N,R,H], one dtype.  N = B for
+ * the rank-4 form and B*Q for the rank-5 form of the reference op.
+ *
+ * Replaces grm_cuda::apply_query_forward (grm/csrc/bindings.cpp:8,
+ * grm/csrc/apply_query.cu:14-75,185-254; math grm/core/cuda_ops.py:257-262).
+ */
+int grmx_apply_query_fwd(const void* memories, const void* queries, void* hidden,
+                         int64_t N, int64_t R, int64_t H, int64_t K, int dtype,
+                         void* stream);
+
+/*
+ * grad_memories[n,r,h,k] = grad_hidden[n,r,h] * queries[n,k]
+ * grad_queries[n,k]      = sum_{r,h} grad_hidden[n,r,h] * memories[n,r,h,k]
+ *
+ * Replaces grm_cuda::apply_query_backward (grm/csrc/bindings.cpp:9,
+ * grm/csrc/apply_query.cu:77-169,256-330).
+ */
+int grmx_apply_query_bwd(const void* grad_hidden, const void* memories, const void* queries,
+                         void* grad_memories, void* grad_queries, int64_t N, int64_t R,
+                         int64_t H, int64_t K, int dtype, void* stream);
+
+/*
+ * out[b,j,:] = memories[b, indices[b,j], :]   for j in [0, J)
+ * memories [B,S,row_elems], indices int64 [B,J], out [B,J,row_elems];
+ * J = R (rank-2 indices) or Q*R (rank-3); row_elems = H*K; elem_size in
+ * bytes (2 or 4).  Index -1 (the empty-slot marker of grmx_topk_route)
+ * yields a zero-filled row; any other index outside [0,S) does too and also
+ * sets the device error word (grmx_device_error_word) instead of faulting.
+ *
+ * Replaces grm_cuda::batched_memory_gather (grm/csrc/bindings.cpp:10,
+ * grm/csrc/batched_gather.cu:14-181; math grm/core/cuda_ops.py:265-284).
+ */
+int grmx_batched_gather(const void* memories, const int64_t* indices, void* out, int64_t B,
+                        int64_t S, int64_t J, int64_t row_elems, int elem_size,
+                        void* stream);
+
+/*
+ * Sparse top-k routing of Q queries per batch row over S segment keys.
+ *
+ *   score[b,q,s] = scale * sum_d queries[b,q,d] * keys[b,s,d]   (fp32 fused
+ *                  multiply-add, d ascending: the summation order is part of
+ *                  the contract so that indices are reproducible bit for bit)
+ *   visible[q] (int32, may be NULL = S): query q sees keys s < visible[q]
+ *   R_q = min(top_k, visible[q]).  When R_q == visible[q] the routes are the
+ *   identity order 0..R_q-1 (no sort); otherwise the R_q highest scores in
+ *   descending order, equal scores resolved to the lower index; NaN ranks
+ *   above every number, -inf below.
+ *   gates = softmax(selected scores / temperature) over the R_q routes.
+ * indices_out int64 [B,Q,top_k] and gates_out fp32 [B,Q,top_k]; slots
+ * r >= R_q hold index -1 and gate 0.  scores_out fp32 [B,Q,S] may be NULL.
+ * Limits: top_k <= 32, S <= 2048.
+ *
+ * Replaces the PyTorch routing of TopKMemoryRetriever.forward
+ * (grm/core/gating_unit.py:54-91) and _route_chunk
+ * (grm/core/paper_grm.py:566-589); the projections stay with the caller.
+ */
+int grmx_topk_route(const float* queries, const float* keys, const int32_t* visible,
+                    int64_t B, int64_t Q, int64_t S, int64_t D, int top_k, float scale,
+                    float temperature, int64_t* indices_out, float* gates_out,
+                    float* scores_out, void* stream);
+
+/*
+ * Selection and gates only, on scores the caller already holds (for example
+ * after applying an attention mask with -inf): same rules as grmx_topk_route
+ * from "visible" onwards.  scores fp32 [B,Q,S].
+ */
+int grmx_topk_select(const float* scores, const int32_t* visible, int64_t B, int64_t Q,
+                     int64_t S, int top_k, float temperature, int64_t* indices_out,
+                     float* gates_out, void* stream);
+
+/*
+ * Retrieval without materialising the gathered matrices:
+ *
+ *   retrieved[b,q,r,:] = archive[b, indices[b,q,r]] @ queries[b,q,:]
+ *   contrib[b,q,:]     = sum_r gates[b,q,r] * retrieved[b,q,r,:]
+ *   fused[b,q,:]       = LayerNorm(online[b,q,:] + contrib[b,q,:]) * ln_weight + ln_bias
+ *
+ * archive fp32 [B,S,H,K]; indices int64 [B,Q,R] (-1 = empty slot, skipped);
+ * gates fp32 [B,Q,R]; queries fp32 [B,Q,K]; online fp32 [B,Q,H].  `mode`
+ * (GRMX_FUSE_*) selects which of the three tensors is written to `out`.
+ * A query whose slots are all empty gets out = online (no LayerNorm) in
+ * GRMX_FUSE_RESIDUAL_LN mode, zeros otherwise -- the reference skips fusion
+ * when no segment is archived (grm/core/paper_grm.py:620-621).
+ * ln_weight / ln_bias may be NULL (identity affine).
+ *
+ * Replaces the chain cuda_batched_memory_gather -> cuda_apply_query ->
+ * RetrievedStateFusion (grm/core/paper_grm.py:229-234,301-307,604-611;
+ * grm/core/aggregator.py:104-105,116-145).
+ */
+int grmx_retrieve_fuse(const float* archive, const int64_t* indices, const float* gates,
+                       const float* queries, const float* online, const float* ln_weight,
+                       const float* ln_bias, float ln_eps, void* out, int64_t B, int64_t S,
+                       int64_t Q, int64_t R, int64_t H, int64_t K, int mode, void* stream);
+
+/*
+ * Device error word: bit 0 = gather index out of range, bit 1 = a bounded
+ * wait inside a kernel gave up.  grmx_device_error_word copies the word of
+ * the current device to *out (synchronises that stream); reset clears it.
+ */
+int grmx_device_error_word(uint32_t* out, void* stream);
+int grmx_device_error_reset(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRMX_H_ */

@@ -1,0 +1,33 @@
+// Parameter block shared by the two kernel families of the linear-memory scan.
+#pragma once
+
+#include "common.cuh"
+
+namespace grmx {
+
+struct ScanParams {
+  const void* keys;      // [B,T,K] io dtype
+  const void* values;    // [B,T,H] io dtype
+  const void* queries;   // [B,T,K] io dtype
+  const void* memory_in; // [B,H,K] state dtype, element strides below
+  void* hidden_out;      // [B,T,H] io dtype
+  void* memory_out;      // [B,H,K] state dtype, dense; may be null
+  int64_t B, T, K, H;
+  int64_t m_row_stride, m_col_stride;
+  float decay;
+  float update_coeff;
+  float hidden_scale;
+  float memory_out_scale;
+  int reverse;
+  int first_step_no_decay;
+};
+
+// fp32 CUDA-core scan: any K <= 256, any H, any T.
+int launch_scan_ffma(const ScanParams& p, int io_dtype, int state_dtype, cudaStream_t stream);
+
+// tcgen05 chunked scan: bf16 operands, fp32 state.  `why` receives the reason
+// when the shape is outside what the tensor-core kernel covers.
+bool scan_tcgen05_supported(const ScanParams& p, int io_dtype, int state_dtype, const char** why);
+int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream);
+
+}  // namespace grmx

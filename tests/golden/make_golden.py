@@ -1,0 +1,218 @@
+"""Generates the golden fixtures in this directory from the reference itself.
+
+Run where a checkout of Sggggt/RNN_with_GRM is available (it is imported, not
+copied):
+
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference /root/reference
+
+Every fixture is an ``.npz`` holding seeded inputs and the outputs of the
+reference's Python implementation on CPU in float32:
+
+* ``chunk_update_*.npz``  -- ``grm.core.cuda_ops._vectorized_chunk_update`` forward and the
+                             autograd gradients of ``h^2.mean() + M^2.mean()`` (the loss of
+                             examples/test_grm.py:88).
+* ``apply_query.npz``     -- ``_fallback_apply_query`` rank 5 and rank 4 with gradients.
+* ``gather.npz``          -- ``_fallback_batched_memory_gather`` on the index tensors of
+                             examples/test_grm.py:203-210.
+* ``retriever_*.npz``     -- ``TopKMemoryRetriever.forward`` (weights included).
+* ``fusion_*.npz``        -- ``RetrievedStateFusion.forward`` for the four weight-bearing modes.
+* ``model_cfg1.npz``      -- ``SegmentRecurrentMemoryModel`` forward on the single-layer
+                             adding-problem configuration (weights, inputs, outputs, final
+                             state and every segment's routing indices and gates).
+"""
+
+from __future__ import annotations
+
+import argparse
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def _normalize(x):
+    return torch.nn.functional.normalize(x, p=2, dim=-1, eps=1e-6)
+
+
+def chunk_case(name, seed, B, T, K, H, decay, zero_state=False):
+    from grm.core.cuda_ops import _vectorized_chunk_update
+
+    g = torch.Generator().manual_seed(seed)
+    k = _normalize(torch.randn(B, T, K, generator=g))
+    v = torch.randn(B, T, H, generator=g)
+    q = _normalize(torch.randn(B, T, K, generator=g))
+    m = torch.zeros(B, H, K) if zero_state else torch.randn(B, H, K, generator=g)
+    leaves = [t.clone().requires_grad_(True) for t in (k, v, q, m)]
+    hidden, m_out = _vectorized_chunk_update(*leaves, decay)
+    loss = hidden.square().mean() + m_out.square().mean()
+    loss.backward()
+    np.savez_compressed(
+        HERE / f"chunk_update_{name}.npz",
+        keys=k.numpy(), values=v.numpy(), queries=q.numpy(), memory=m.numpy(), decay=np.float64(decay),
+        hidden=hidden.detach().numpy(), memory_out=m_out.detach().numpy(),
+        grad_hidden=(2.0 * hidden.detach() / hidden.numel()).numpy(),
+        grad_memory_out=(2.0 * m_out.detach() / m_out.numel()).numpy(),
+        grad_keys=leaves[0].grad.numpy(), grad_values=leaves[1].grad.numpy(),
+        grad_queries=leaves[2].grad.numpy(), grad_memory=leaves[3].grad.numpy(),
+    )
+
+
+def apply_query_case():
+    from grm.core.cuda_ops import _fallback_apply_query
+
+    g = torch.Generator().manual_seed(11)
+    out = {}
+    for tag, mshape, qshape in (("r5", (2, 3, 4, 5, 6), (2, 3, 6)), ("r4", (3, 4, 16, 8), (3, 8))):
+        mem = torch.randn(*mshape, generator=g).requires_grad_(True)
+        qry = _normalize(torch.randn(*qshape, generator=g)).requires_grad_(True)
+        hid = _fallback_apply_query(mem, qry)
+        hid.square().mean().backward()
+        out.update({
+            f"{tag}_memories": mem.detach().numpy(), f"{tag}_queries": qry.detach().numpy(),
+            f"{tag}_hidden": hid.detach().numpy(),
+            f"{tag}_grad_hidden": (2.0 * hid.detach() / hid.numel()).numpy(),
+            f"{tag}_grad_memories": mem.grad.numpy(), f"{tag}_grad_queries": qry.grad.numpy(),
+        })
+    np.savez_compressed(HERE / "apply_query.npz", **out)
+
+
+def gather_case():
+    from grm.core.cuda_ops import _fallback_batched_memory_gather
+
+    g = torch.Generator().manual_seed(12)
+    mem = torch.randn(2, 7, 4, 5, generator=g)
+    # the literal index tensors of the reference's own gather test (examples/test_grm.py:203-210)
+    idx3 = torch.tensor([[[1, 3], [2, 5], [0, 6]], [[4, 2], [1, 0], [3, 5]]], dtype=torch.long)
+    idx2 = torch.tensor([[0, 2, 4], [1, 3, 5]], dtype=torch.long)
+    np.savez_compressed(
+        HERE / "gather.npz", memories=mem.numpy(), idx3=idx3.numpy(), idx2=idx2.numpy(),
+        out3=_fallback_batched_memory_gather(mem, idx3).numpy(),
+        out2=_fallback_batched_memory_gather(mem, idx2).numpy(),
+    )
+
+
+def retriever_cases():
+    from grm.core.gating_unit import TopKMemoryRetriever
+
+    for name, S, top_k, offset, use_mask in (("topk", 9, 3, 0, False), ("identity", 3, 4, 0, False),
+                                            ("causal", 8, 3, 5, False), ("masked", 8, 3, 0, True)):
+        torch.manual_seed(21)
+        mod = TopKMemoryRetriever(query_dim=6, key_dim=6, hidden_dim=6, retrieval_top_k=top_k, dropout=0.0).eval()
+        g = torch.Generator().manual_seed(22)
+        query = torch.randn(5, 6, generator=g)
+        keys = torch.randn(5, S, 6, generator=g)
+        mask = None
+        if use_mask:
+            mask = torch.ones(5, S, dtype=torch.bool)
+            mask[:, 1] = False
+            mask[2, 4:] = False
+        with torch.no_grad():
+            gates, idx, scores = mod(query, keys, segment_offset=offset, attention_mask=mask)
+        # margin between the last selected and the best rejected score, to make sure the
+        # fixture does not sit on a rounding-sensitive tie
+        finite = torch.where(torch.isfinite(scores), scores, torch.full_like(scores, -1e30))
+        srt = torch.sort(finite, dim=-1, descending=True).values
+        kk = min(top_k, S)
+        margin = float((srt[:, kk - 1] - srt[:, kk]).min()) if kk < S else float("inf")
+        assert margin > 1e-4, f"retriever fixture {name} has a near-tie (margin {margin})"
+        np.savez_compressed(
+            HERE / f"retriever_{name}.npz",
+            query=query.numpy(), keys=keys.numpy(), segment_offset=np.int64(offset), top_k=np.int64(top_k),
+            attention_mask=(mask.numpy() if mask is not None else np.zeros((0,), dtype=bool)),
+            w_query=mod.query_projection.weight.detach().numpy(), w_key=mod.key_projection.weight.detach().numpy(),
+            gates=gates.numpy(), indices=idx.numpy(), scores=scores.numpy(),
+        )
+
+
+def fusion_cases():
+    from grm.core.aggregator import RetrievedStateFusion
+
+    for mode in ("residual", "concat", "gate", "linear"):
+        torch.manual_seed(31)
+        mod = RetrievedStateFusion(hidden_size=16, retrieval_fusion_mode=mode, dropout=0.0).eval()
+        with torch.no_grad():
+            mod.layer_norm.weight.uniform_(0.5, 1.5)
+            mod.layer_norm.bias.uniform_(-0.5, 0.5)
+        g = torch.Generator().manual_seed(32)
+        online = torch.randn(7, 16, generator=g)
+        retrieved = torch.randn(7, 3, 16, generator=g)
+        gates = torch.softmax(torch.randn(7, 3, generator=g), dim=-1)
+        with torch.no_grad():
+            fused = mod(h_online=online, cached_states=retrieved, gates=gates)
+        params = {f"param::{k}": v.detach().numpy() for k, v in mod.state_dict().items()}
+        np.savez_compressed(HERE / f"fusion_{mode}.npz", online=online.numpy(), retrieved=retrieved.numpy(),
+                            gates=gates.numpy(), fused=fused.numpy(), eps=np.float64(mod.layer_norm.eps), **params)
+
+
+def adding_problem_inputs(batch, seq_len, seed):
+    """Channel 0 ~ U[0,1); channel 1 marks two positions, one in each half."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.zeros(batch, seq_len, 2)
+    x[:, :, 0] = torch.rand(batch, seq_len, generator=g)
+    half = seq_len // 2
+    first = torch.randint(0, half, (batch,), generator=g)
+    second = torch.randint(half, seq_len, (batch,), generator=g)
+    x[torch.arange(batch), first, 1] = 1.0
+    x[torch.arange(batch), second, 1] = 1.0
+    return x
+
+
+def model_cfg1_case():
+    from grm.core.paper_grm import SegmentRecurrentMemoryModel
+
+    torch.manual_seed(0)
+    model = SegmentRecurrentMemoryModel(
+        input_size=2, hidden_size=128, output_size=1, segment_length=128, memory_key_dim=64,
+        retrieval_top_k=2, memory_capacity_segments=8, memory_storage_dtype=torch.float32,
+        recomputation_ratio=0.0, dropout=0.0, cuda_cpp_debug_fallback=True,
+    ).eval()
+    x = adding_problem_inputs(2, 512, seed=0)
+    routes = []
+    original = model._route_chunk
+
+    def recording_route(batch_inputs, segment_keys):
+        gates, idx = original(batch_inputs, segment_keys)
+        routes.append((gates.clone(), idx.clone()))
+        return gates, idx
+
+    model._route_chunk = recording_route
+    with torch.no_grad():
+        outputs, h_final, memory_final, aux = model(x, reset_memory=True, return_hidden_states=True)
+    payload = {f"param::{k}": v.detach().numpy() for k, v in model.state_dict().items()
+               if isinstance(v, torch.Tensor) and not k.startswith("memory_bank")}
+    for i, (gates, idx) in enumerate(routes):
+        payload[f"route{i + 1}_gates"] = gates.numpy()
+        payload[f"route{i + 1}_indices"] = idx.numpy()
+    np.savez_compressed(
+        HERE / "model_cfg1.npz", x=x.numpy(), outputs=outputs.numpy(), h_final=h_final.numpy(),
+        memory_final=memory_final.numpy(), hidden_states=aux["hidden_states"].numpy(),
+        num_segments=np.int64(aux["num_segments"]), **payload,
+    )
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--reference", type=Path, default=Path("/root/reference"))
+    args = parser.parse_args(argv)
+    sys.dont_write_bytecode = True
+    sys.path.insert(0, str(args.reference))
+    torch.set_num_threads(1)
+    chunk_case("small", 1, B=2, T=8, K=8, H=16, decay=0.97)        # shape of examples/test_grm.py:29-37
+    chunk_case("ragged", 2, B=3, T=67, K=6, H=5, decay=0.9)
+    chunk_case("cfg1", 3, B=2, T=128, K=64, H=128, decay=0.97, zero_state=True)
+    chunk_case("long", 4, B=1, T=300, K=32, H=48, decay=0.999)
+    apply_query_case()
+    gather_case()
+    retriever_cases()
+    fusion_cases()
+    model_cfg1_case()
+    total = sum(p.stat().st_size for p in HERE.glob("*.npz"))
+    print(f"wrote {len(list(HERE.glob('*.npz')))} fixtures, {total / 1024:.0f} KiB")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
