@@ -1,0 +1,317 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the oracle.
+
+Tolerances (relative to the largest reference magnitude, ``oracle.rel_err``):
+float32 mode 1e-5; bf16/fp16 inputs with float32 state 2e-2; gathered
+matrices, routing scores and top-k indices bit for bit.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import grm_oracle as go
+from rnn_with_grm_b200 import cabi
+
+import grmx_calls as gx
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5
+FP32_GRAD_TOL = 5e-5   # the golden gradients are float32 results of the reference (see test_oracle.py)
+LOWP_TOL = 2e-2
+DEV = "cuda:0"
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    return t.to(dtype) if dtype is not None else t
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+def close(actual, expected, tol):
+    err = go.rel_err(host(actual) if isinstance(actual, torch.Tensor) else actual, expected)
+    assert err < tol, f"rel err {err:.3e} >= {tol:.1e}"
+
+
+def make_chunk(seed, B, T, K, H, zero_state=False):
+    rng = np.random.default_rng(seed)
+    k = rng.standard_normal((B, T, K)).astype(np.float32)
+    q = rng.standard_normal((B, T, K)).astype(np.float32)
+    k /= np.maximum(np.linalg.norm(k, axis=-1, keepdims=True), 1e-6)
+    q /= np.maximum(np.linalg.norm(q, axis=-1, keepdims=True), 1e-6)
+    v = rng.standard_normal((B, T, H)).astype(np.float32)
+    m = np.zeros((B, H, K), np.float32) if zero_state else rng.standard_normal((B, H, K)).astype(np.float32)
+    return k, v, q, m
+
+
+# --------------------------------------------------------------------------- chunk scan, fp32
+
+@pytest.mark.parametrize("name", ["small", "ragged", "cfg1", "long"])
+def test_chunk_scan_matches_reference_fixture(golden, name):
+    g = golden(f"chunk_update_{name}")
+    decay = float(g["decay"])
+    hidden, m_out = gx.chunk_scan_fwd(dev(g["keys"]), dev(g["values"]), dev(g["queries"]), dev(g["memory"]),
+                                      decay, cabi.PATH_FFMA)
+    close(hidden, g["hidden"], FP32_TOL)
+    close(m_out, g["memory_out"], FP32_TOL)
+    grads = gx.chunk_scan_bwd(dev(g["grad_hidden"]), dev(g["grad_memory_out"]), dev(g["keys"]), dev(g["values"]),
+                              dev(g["queries"]), dev(g["memory"]), decay, cabi.PATH_FFMA)
+    for got, key in zip(grads, ("grad_keys", "grad_values", "grad_queries", "grad_memory")):
+        close(got, g[key], FP32_GRAD_TOL)
+
+
+@pytest.mark.parametrize("K", [1, 2, 7, 8, 16, 33, 64, 128, 200])
+@pytest.mark.parametrize("H,T", [(1, 1), (5, 17), (32, 16), (33, 100), (128, 64)])
+def test_chunk_scan_shape_sweep(K, H, T):
+    k, v, q, m = make_chunk(K * 1000 + H * 10 + T, 2, T, K, H)
+    want_h, want_m = go.chunk_update_sequential(k, v, q, m, 0.97)
+    hidden, m_out = gx.chunk_scan_fwd(dev(k), dev(v), dev(q), dev(m), 0.97, cabi.PATH_FFMA)
+    close(hidden, want_h, FP32_TOL)
+    close(m_out, want_m, FP32_TOL)
+
+
+def test_chunk_scan_backward_seeded():
+    k, v, q, m = make_chunk(77, 3, 45, 24, 40)
+    rng = np.random.default_rng(78)
+    gh = rng.standard_normal((3, 45, 40)).astype(np.float32)
+    gm = rng.standard_normal((3, 40, 24)).astype(np.float32)
+    want = go.chunk_update_backward(gh, gm, k, v, q, m, 0.9)
+    got = gx.chunk_scan_bwd(dev(gh), dev(gm), dev(k), dev(v), dev(q), dev(m), 0.9, cabi.PATH_FFMA)
+    for a, b in zip(got, want):
+        close(a, b, FP32_TOL)
+
+
+def test_chunk_scan_degenerate_calls():
+    k, v, q, m = make_chunk(5, 2, 4, 8, 16)
+    # zero tokens: state passes through (grm/csrc/grm_cuda.cpp:59-65)
+    hidden, m_out = gx.chunk_scan_fwd(dev(k[:, :0]), dev(v[:, :0]), dev(q[:, :0]), dev(m), 0.97)
+    assert hidden.shape == (2, 0, 16) and torch.equal(m_out, dev(m))
+    gk, gv, gq, gmem = gx.chunk_scan_bwd(dev(v[:, :0]), dev(m), dev(k[:, :0]), dev(v[:, :0]), dev(q[:, :0]),
+                                         dev(m), 0.97)
+    assert torch.equal(gmem, dev(m))
+    # zero batch rows
+    hidden, m_out = gx.chunk_scan_fwd(dev(k[:0]), dev(v[:0]), dev(q[:0]), dev(m[:0]), 0.97)
+    assert hidden.numel() == 0 and m_out.numel() == 0
+
+
+def test_chunk_scan_is_independent_of_call_splitting():
+    k, v, q, m = make_chunk(9, 4, 256, 64, 64)
+    tk, tv, tq, tm = dev(k), dev(v), dev(q), dev(m)
+    whole_h, whole_m = gx.chunk_scan_fwd(tk, tv, tq, tm, 0.97, cabi.PATH_FFMA)
+    state, pieces = tm, []
+    for s in range(0, 256, 64):
+        h, state = gx.chunk_scan_fwd(tk[:, s:s + 64].contiguous(), tv[:, s:s + 64].contiguous(),
+                                     tq[:, s:s + 64].contiguous(), state, 0.97, cabi.PATH_FFMA)
+        pieces.append(h)
+    # the fp32 kernel is token-serial, so splitting the call changes nothing, bit for bit
+    assert torch.equal(torch.cat(pieces, dim=1), whole_h) and torch.equal(state, whole_m)
+    again_h, again_m = gx.chunk_scan_fwd(tk, tv, tq, tm, 0.97, cabi.PATH_FFMA)
+    assert torch.equal(again_h, whole_h) and torch.equal(again_m, whole_m)
+
+
+@pytest.mark.parametrize("io,state,tol", [(torch.bfloat16, torch.float32, LOWP_TOL),
+                                         (torch.bfloat16, torch.bfloat16, 5e-2),
+                                         (torch.float16, torch.float32, LOWP_TOL),
+                                         (torch.float16, torch.float16, LOWP_TOL)])
+def test_chunk_scan_low_precision_inputs(io, state, tol):
+    k, v, q, m = make_chunk(21, 3, 96, 64, 64)
+    tk, tv, tq = dev(k, io), dev(v, io), dev(q, io)
+    tm = dev(m, state)
+    # oracle on exactly the rounded inputs, in float64
+    want_h, want_m = go.chunk_update_sequential(host(tk), host(tv), host(tq), host(tm), 0.97)
+    hidden, m_out = gx.chunk_scan_fwd(tk, tv, tq, tm, 0.97, cabi.PATH_FFMA)
+    assert hidden.dtype == io and m_out.dtype == state
+    close(hidden, want_h, tol)
+    close(m_out, want_m, tol)
+
+
+@pytest.mark.parametrize("reverse", [False, True])
+@pytest.mark.parametrize("no_decay_first", [False, True])
+def test_linear_scan_general_form(reverse, no_decay_first):
+    k, v, q, m = make_chunk(31, 2, 37, 12, 20)
+    want_h, want_m = go.linear_scan(k, v, q, m, 0.93, 0.31, hidden_scale=1.7, memory_out_scale=0.6,
+                                    reverse=reverse, first_step_no_decay=no_decay_first)
+    hidden, m_out = gx.linear_scan(dev(k), dev(v), dev(q), dev(m), 0.93, 0.31, 1.7, 0.6, reverse, no_decay_first,
+                                   cabi.PATH_FFMA)
+    close(hidden, want_h, FP32_TOL)
+    close(m_out, want_m, FP32_TOL)
+    # the same state handed over transposed
+    m_t = np.ascontiguousarray(m.transpose(0, 2, 1))
+    hidden_t, m_out_t = gx.linear_scan(dev(k), dev(v), dev(q), dev(m_t), 0.93, 0.31, 1.7, 0.6, reverse,
+                                       no_decay_first, cabi.PATH_FFMA, transposed_state=True)
+    assert torch.equal(hidden_t, hidden) and torch.equal(m_out_t, m_out)
+
+
+def test_chunk_scan_rejects_bad_arguments():
+    lib = cabi.load()
+    k, v, q, m = (dev(a) for a in make_chunk(1, 1, 4, 8, 8))
+    out_h, out_m = torch.empty_like(v), torch.empty_like(m)
+    args = [cabi.ptr(k), cabi.ptr(v), cabi.ptr(q), cabi.ptr(m), cabi.ptr(out_h), cabi.ptr(out_m)]
+    assert lib.grmx_chunk_scan_fwd(*args, 1, 4, 0, 8, 0.97, 0, 0, 0, None) == 1          # K == 0
+    assert lib.grmx_chunk_scan_fwd(*args, 1, 4, 8, 8, 0.97, 7, 0, 0, None) == 1          # bad dtype
+    assert lib.grmx_chunk_scan_fwd(*args, 1, 4, 8, 8, 0.97, 0, 1, 0, None) == 1          # state dtype != io, != f32
+    assert lib.grmx_chunk_scan_fwd(*args, 1, 4, 300, 8, 0.97, 0, 0, 1, None) == 2        # K > 256 unsupported
+    assert b"key dim" in lib.grmx_last_error()
+    with pytest.raises(cabi.GrmxError):
+        gx.chunk_scan_fwd(k, v, q, m, 0.97, path=9)
+
+
+# --------------------------------------------------------------------------- apply query
+
+def test_apply_query_matches_reference_fixture(golden):
+    g = golden("apply_query")
+    for tag in ("r5", "r4"):
+        mem, qry = dev(g[f"{tag}_memories"]), dev(g[f"{tag}_queries"])
+        close(gx.apply_query_fwd(mem, qry), g[f"{tag}_hidden"], FP32_TOL)
+        gm, gq = gx.apply_query_bwd(dev(g[f"{tag}_grad_hidden"]), mem, qry)
+        close(gm, g[f"{tag}_grad_memories"], FP32_TOL)
+        close(gq, g[f"{tag}_grad_queries"], FP32_TOL)
+
+
+@pytest.mark.parametrize("shape", [(3, 2, 64, 64), (2, 5, 4, 128, 64), (4, 1, 7, 6), (2, 3, 300, 20), (1, 2, 9, 513)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, LOWP_TOL), (torch.float16, LOWP_TOL)])
+def test_apply_query_shapes_and_dtypes(shape, dtype, tol):
+    rng = np.random.default_rng(sum(shape))
+    mem = dev(rng.standard_normal(shape).astype(np.float32), dtype)
+    qry = dev(rng.standard_normal(shape[:-3] + shape[-1:]).astype(np.float32), dtype)
+    want = go.apply_query(host(mem), host(qry))
+    close(gx.apply_query_fwd(mem, qry), want, tol)
+    gh = dev(rng.standard_normal(shape[:-1]).astype(np.float32), dtype)
+    want_gm, want_gq = go.apply_query_backward(host(gh), host(mem), host(qry))
+    gm, gq = gx.apply_query_bwd(gh, mem, qry)
+    close(gm, want_gm, tol)
+    close(gq, want_gq, tol)
+
+
+# --------------------------------------------------------------------------- gather
+
+def test_gather_matches_reference_fixture_bit_for_bit(golden):
+    g = golden("gather")
+    mem = dev(g["memories"])
+    assert np.array_equal(host(gx.batched_gather(mem, dev(g["idx3"]))), g["out3"])
+    assert np.array_equal(host(gx.batched_gather(mem, dev(g["idx2"]))), g["out2"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("hk", [(64, 64), (5, 3), (128, 64), (7, 2)])
+def test_gather_random_bit_exact(dtype, hk):
+    rng = np.random.default_rng(hk[0])
+    B, S, Q, R = 3, 11, 5, 4
+    mem = dev(rng.standard_normal((B, S) + hk).astype(np.float32), dtype)
+    idx = dev(rng.integers(0, S, size=(B, Q, R)))
+    out = gx.batched_gather(mem, idx)
+    want, bad = oracle.c_batched_gather(mem.cpu().view(torch.int16 if dtype != torch.float32 else torch.int32).numpy(),
+                                        idx.cpu().numpy())
+    assert bad == 0
+    got = out.cpu().view(torch.int16 if dtype != torch.float32 else torch.int32).numpy()
+    assert np.array_equal(got, want)
+
+
+def test_gather_empty_slots_and_bad_indices():
+    lib = cabi.load()
+    cabi.check(lib.grmx_device_error_reset(cabi.current_stream()))
+    mem = dev(np.arange(2 * 3 * 4 * 4, dtype=np.float32).reshape(2, 3, 4, 4))
+    out = gx.batched_gather(mem, dev(np.array([[2, -1], [0, 1]])))
+    assert torch.equal(out[0, 0], mem[0, 2]) and not out[0, 1].any()
+    assert cabi.device_error_word() == 0                      # -1 is the empty-slot marker
+    out = gx.batched_gather(mem, dev(np.array([[3, 0], [0, -2]])))
+    assert not out[0, 0].any() and not out[1, 1].any() and torch.equal(out[0, 1], mem[0, 0])
+    assert cabi.device_error_word() & 1
+    cabi.check(lib.grmx_device_error_reset(cabi.current_stream()))
+    assert cabi.device_error_word() == 0
+    # empty archive / empty index list
+    assert gx.batched_gather(mem[:, :0], dev(np.zeros((2, 0), dtype=np.int64))).shape == (2, 0, 4, 4)
+
+
+# --------------------------------------------------------------------------- routing
+
+def test_topk_route_bit_exact_against_c_oracle():
+    rng = np.random.default_rng(41)
+    B, Q, S, D, top_k = 6, 9, 32, 64, 4
+    qv = rng.standard_normal((B, Q, D)).astype(np.float32)
+    kv = rng.standard_normal((B, S, D)).astype(np.float32)
+    visible = np.array([0, 1, 3, 4, 5, 9, 17, 32, 40], dtype=np.int32)
+    want_scores = oracle.c_route_scores(qv, kv, 0.125)
+    want_idx, want_gates = oracle.c_topk_select(want_scores, top_k, 0.7, visible)
+    idx, gates, scores = gx.topk_route(dev(qv), dev(kv), top_k, 0.125, 0.7, dev(visible))
+    assert np.array_equal(host(scores), want_scores)          # same fused multiply-add order
+    assert np.array_equal(idx.cpu().numpy(), want_idx)
+    close(gates, want_gates, FP32_TOL)
+    idx2, gates2, _ = gx.topk_route(dev(qv), dev(kv), top_k, 0.125, 0.7, dev(visible), want_scores=False)
+    assert torch.equal(idx2, idx) and torch.equal(gates2, gates)
+
+
+def test_topk_matches_reference_retriever_fixtures(golden):
+    for name in ("topk", "identity"):
+        g = golden(f"retriever_{name}")
+        pq = torch.nn.functional.linear(dev(g["query"]), dev(g["w_query"]))
+        pk = torch.nn.functional.linear(dev(g["keys"]), dev(g["w_key"]))
+        top_k = int(g["top_k"])
+        idx, gates, scores = gx.topk_route(pq[:, None, :].contiguous(), pk.contiguous(), top_k,
+                                           1.0 / np.sqrt(g["w_query"].shape[0]))
+        R = g["indices"].shape[1]
+        assert np.array_equal(idx.cpu().numpy()[:, 0, :R], g["indices"])
+        close(gates[:, 0, :R], g["gates"], FP32_TOL)
+        close(scores[:, 0], g["scores"], FP32_TOL)
+
+
+def test_topk_select_ties_nan_and_masks():
+    scores = np.zeros((1, 3, 8), dtype=np.float32)
+    scores[0, 1, [2, 5]] = 1.0
+    scores[0, 2] = [np.nan, -np.inf, 3.0, 3.0, -0.0, 0.0, -np.inf, 2.0]
+    idx, gates = gx.topk_select(dev(scores), 4)
+    assert idx.cpu().tolist() == [[[0, 1, 2, 3], [2, 5, 0, 1], [0, 2, 3, 7]]]
+    assert torch.isnan(gates[0, 2]).all() and torch.allclose(gates[0, 0], torch.full((4,), 0.25, device=DEV))
+    rng = np.random.default_rng(43)
+    big = rng.standard_normal((4, 7, 300)).astype(np.float32)
+    big[:, :, ::7] = -np.inf
+    big[1, 2, :] = 0.5                                          # all equal
+    want_idx, want_gates = oracle.c_topk_select(big, 8, 2.0)
+    idx, gates = gx.topk_select(dev(big), 8, 2.0)
+    assert np.array_equal(idx.cpu().numpy(), want_idx)
+    close(gates, want_gates, FP32_TOL)
+    # more routes requested than keys: identity order, padded
+    idx, gates = gx.topk_select(dev(big[:, :, :3]), 8)
+    assert idx[0, 0].cpu().tolist() == [0, 1, 2, -1, -1, -1, -1, -1] and float(gates[0, 0, 3:].abs().sum()) == 0.0
+
+
+# --------------------------------------------------------------------------- fused retrieval
+
+@pytest.mark.parametrize("H,K", [(64, 64), (16, 8), (20, 6), (128, 64), (512, 64)])
+def test_retrieve_fuse_modes(H, K):
+    rng = np.random.default_rng(H + K)
+    B, S, Q, R = 3, 9, 5, 4
+    archive = rng.standard_normal((B, S, H, K)).astype(np.float32)
+    idx = rng.integers(0, S, size=(B, Q, R))
+    idx[1, 2] = -1
+    idx[0, 1, 2:] = -1
+    gates = rng.random((B, Q, R)).astype(np.float32)
+    queries = rng.standard_normal((B, Q, K)).astype(np.float32)
+    online = rng.standard_normal((B, Q, H)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, H).astype(np.float32)
+    b = rng.uniform(-0.5, 0.5, H).astype(np.float32)
+    t = dict(archive=dev(archive), indices=dev(idx), gates=dev(gates), queries=dev(queries))
+    for mode, name in ((cabi.FUSE_RETRIEVED, "retrieved"), (cabi.FUSE_CONTRIB, "contrib")):
+        got = gx.retrieve_fuse(**t, mode=mode)
+        close(got, go.retrieve_fuse(archive, idx, gates, queries, mode=name), FP32_TOL)
+    got = gx.retrieve_fuse(**t, online=dev(online), ln_weight=dev(w), ln_bias=dev(b), mode=cabi.FUSE_RESIDUAL_LN)
+    close(got, go.retrieve_fuse(archive, idx, gates, queries, online, w, b), FP32_TOL)
+    assert torch.equal(got[1, 2], dev(online)[1, 2])          # no archived segment: online passes through
+    got = gx.retrieve_fuse(**t, online=dev(online), mode=cabi.FUSE_RESIDUAL_LN)
+    close(got, go.retrieve_fuse(archive, idx, gates, queries, online), FP32_TOL)
+
+
+def test_retrieve_fuse_equals_gather_then_apply(golden):
+    rng = np.random.default_rng(51)
+    B, S, Q, R, H, K = 2, 6, 4, 3, 64, 64
+    archive = dev(rng.standard_normal((B, S, H, K)).astype(np.float32))
+    idx = dev(rng.integers(0, S, size=(B, Q, R)))
+    queries = dev(rng.standard_normal((B, Q, K)).astype(np.float32))
+    gathered = gx.batched_gather(archive, idx)
+    two_step = gx.apply_query_fwd(gathered, queries)
+    fused = gx.retrieve_fuse(archive, idx, None, queries, mode=cabi.FUSE_RETRIEVED)
+    assert torch.equal(fused, two_step)
