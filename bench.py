@@ -263,7 +263,7 @@ def run_engine(args, rank, world, device):
         },
         "clocks": sampler.summary([window, e2e_window]),
     }
-    if world == 1:
+    if world == 1 and not args.skip_extras:
         result["cpu_baseline"] = cpu_baseline(sample_rows=rows, reps=3)
         result["other_workloads"] = other_workloads(lib, device, hbm_peak)
     return result
@@ -427,6 +427,8 @@ def main(argv=None) -> int:
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", choices=["engine", "reference"], default="engine")
+    parser.add_argument("--skip-extras", action="store_true",
+                        help="main workload only: no CPU baseline, no other workloads (small footprint for profiling)")
     args = parser.parse_args(argv)
     args.warmup = max(args.warmup, 3)
 

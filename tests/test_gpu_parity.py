@@ -315,3 +315,66 @@ def test_retrieve_fuse_equals_gather_then_apply(golden):
     two_step = gx.apply_query_fwd(gathered, queries)
     fused = gx.retrieve_fuse(archive, idx, None, queries, mode=cabi.FUSE_RETRIEVED)
     assert torch.equal(fused, two_step)
+
+
+# --------------------------------------------------------------------------- chunk scan, tcgen05 path
+
+def _tc_case(seed, B, T, decay, zero_state):
+    k, v, q, m = make_chunk(seed, B, T, 64, 64, zero_state=zero_state)
+    tk, tv, tq = dev(k, torch.bfloat16), dev(v, torch.bfloat16), dev(q, torch.bfloat16)
+    tm = dev(m)
+    want = go.chunk_update_sequential(host(tk), host(tv), host(tq), m, decay)
+    return (tk, tv, tq, tm), want
+
+
+@pytest.mark.parametrize("B,T,decay,zero_state", [(1, 128, 0.97, True), (2, 256, 0.97, False), (3, 1024, 0.9, False),
+                                                  (5, 384, 0.999, False), (2, 512, 0.5, False), (2, 256, 0.0, False),
+                                                  (2, 256, 1.0, False)])
+def test_tcgen05_scan_matches_oracle(B, T, decay, zero_state):
+    args, (want_h, want_m) = _tc_case(B * 7 + T, B, T, decay, zero_state)
+    hidden, m_out = gx.chunk_scan_fwd(*args, decay, cabi.PATH_TCGEN05)
+    assert hidden.dtype == torch.bfloat16 and m_out.dtype == torch.float32
+    close(hidden, want_h, LOWP_TOL)
+    close(m_out, want_m, LOWP_TOL)
+    assert cabi.device_error_word() == 0
+    # the two kernel families agree with each other far inside the tolerance
+    ffma_h, ffma_m = gx.chunk_scan_fwd(*args, decay, cabi.PATH_FFMA)
+    close(hidden, host(ffma_h), LOWP_TOL)
+    close(m_out, host(ffma_m), LOWP_TOL)
+
+
+def test_tcgen05_scan_full_size_kernel_alone_config():
+    # B=8 x H=8 rows, T=2048, d_k=d_v=64, zero start state: the benchmark's workload
+    args, (want_h, want_m) = _tc_case(2, 64, 2048, 0.97, True)
+    hidden, m_out = gx.chunk_scan_fwd(*args, 0.97, cabi.PATH_AUTO)
+    close(hidden, want_h, LOWP_TOL)
+    close(m_out, want_m, LOWP_TOL)
+    again_h, again_m = gx.chunk_scan_fwd(*args, 0.97, cabi.PATH_AUTO)
+    assert torch.equal(again_h, hidden) and torch.equal(again_m, m_out)          # run-to-run deterministic
+    # one call over T equals 16 calls of 128 tokens carrying the state
+    state, pieces = args[3], []
+    for s in range(0, 2048, 128):
+        h, state = gx.chunk_scan_fwd(*(t[:, s:s + 128].contiguous() for t in args[:3]), state, 0.97, cabi.PATH_TCGEN05)
+        pieces.append(h)
+    assert torch.equal(torch.cat(pieces, dim=1), hidden) and torch.equal(state, m_out)
+
+
+def test_tcgen05_scan_is_linear_in_values_and_state():
+    # size-independent property: the scan is linear in (values, start state)
+    (tk, tv, tq, tm), _ = _tc_case(9, 4, 512, 0.97, False)
+    h1, m1 = gx.chunk_scan_fwd(tk, tv, tq, tm, 0.97, cabi.PATH_TCGEN05)
+    h2, m2 = gx.chunk_scan_fwd(tk, (tv.float() * 2).to(torch.bfloat16), tq, tm * 2, 0.97, cabi.PATH_TCGEN05)
+    close(h2, 2 * host(h1), LOWP_TOL)
+    close(m2, 2 * host(m1), 1e-6)
+
+
+def test_tcgen05_path_refuses_what_it_does_not_cover():
+    k, v, q, m = make_chunk(1, 1, 100, 64, 64)
+    with pytest.raises(cabi.GrmxError, match="multiple of 128"):
+        gx.chunk_scan_fwd(dev(k, torch.bfloat16), dev(v, torch.bfloat16), dev(q, torch.bfloat16), dev(m), 0.97,
+                          cabi.PATH_TCGEN05)
+    with pytest.raises(cabi.GrmxError, match="bf16"):
+        gx.chunk_scan_fwd(dev(k), dev(v), dev(q), dev(m), 0.97, cabi.PATH_TCGEN05)
+    # auto falls back to the fp32 kernel for the same request
+    hidden, _ = gx.chunk_scan_fwd(dev(k), dev(v), dev(q), dev(m), 0.97, cabi.PATH_AUTO)
+    close(hidden, go.chunk_update_sequential(k, v, q, m, 0.97)[0], FP32_TOL)
