@@ -35,6 +35,7 @@ CUDA_SOURCES = [
     "chunk_scan.cu",
     "chunk_scan_ffma.cu",
     "chunk_scan_tc.cu",
+    "chunk_scan_tc_pipe.cu",
     "apply_query.cu",
     "gather.cu",
     "topk_route.cu",

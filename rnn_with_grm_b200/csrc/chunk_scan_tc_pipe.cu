@@ -1,0 +1,457 @@
+// Warp-specialised, pipelined tcgen05 kernel of the linear-memory scan
+// (d_k = d_v = 64, bf16 operands, fp32 state in TMEM, chunks of 128 tokens).
+//
+// Same four products per chunk as the synchronous kernel in chunk_scan_tc.cu
+//   S = Q Kc^T,  O2 = Q Mb^T,  M += Vw^T Kc,  O1 = P Vc
+// but the roles run concurrently and only the tiny state hand-off is serial:
+//
+//   warp 9     TMA producer: q/k/v tiles of chunk c into a 3-stage ring
+//   warp 8     MMA issuer:   S_{c+1} | O2_c, M_c | O1_c  (one thread, tcgen05.mma)
+//   warps 0-3  "P" group:    Vw_{c+1} (scaled copy of Vc) and S_c -> P_c (decay mask, bf16)
+//   warps 4-7  "E" group:    state pass (M_c -> bf16 copy, rescale) and epilogue (O1_c, O2_c -> HBM)
+//
+// TMEM (512 columns): two S/O1 buffers, two O2 buffers, the state.  Every
+// hand-off is an mbarrier; producers and consumers are never more than one
+// phase apart (see the protocol comment in the kernel), and every wait is
+// bounded: on expiry the CTA-wide abort flag is raised, all roles drain, the
+// error word gets bit 1, TMEM is freed and the kernel returns.
+//
+// Math: closed form of the reference chunk (grm/core/cuda_ops.py:218-254),
+// state carried across chunks as in grm/csrc/grm_cuda.cpp:67-83.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "scan.cuh"
+#include "tc_ptx.cuh"
+
+namespace grmx {
+namespace {
+
+using namespace tc;
+
+constexpr int kChunk = 128;
+constexpr int kD = 64;                 // d_k == d_v
+constexpr int kStages = 3;
+constexpr int kThreads = 320;
+constexpr int kMmaWarp = 8;
+constexpr int kTmaWarp = 9;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColSO = 0;         // + 128 * buffer : S (128 cols), then O1 (first 64 cols)
+constexpr uint32_t kColO2 = 256;       // + 64 * buffer
+constexpr uint32_t kColM = 384;        // state: 64 columns, lanes 0-15 of each quarter
+
+constexpr int kTileBytes = kChunk * kD * 2;          // 16 KiB: one [128 x 64] bf16 tile
+constexpr int kStageBytes = 3 * kTileBytes;          // q, k, v
+constexpr int kOffStage = 0;
+constexpr int kOffP = kStages * kStageBytes;         // [128 x 128] bf16 as two K-major blocks
+constexpr int kOffVw = kOffP + 2 * kTileBytes;       // two buffers
+constexpr int kOffMb = kOffVw + 2 * kTileBytes;      // [64 x 64] bf16
+constexpr int kOffWtab = kOffMb + kD * kD * 2;       // float[256]: weight(d), d = i - j in [-128, 127]
+constexpr int kOffPow = kOffWtab + 256 * 4;          // float[kChunk + 4]: decay^j
+constexpr int kOffBars = kOffPow + (kChunk + 4) * 4;
+constexpr int kNumBars = 20;
+constexpr int kOffMisc = kOffBars + kNumBars * 8;
+constexpr int kSmemTotal = kOffMisc + 32;
+constexpr int kSmemAlloc = kSmemTotal + 1024;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// descriptor + byte offset (the start-address field holds addr >> 4 in its low 14 bits)
+__device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+
+__global__ void __launch_bounds__(kThreads, 1)
+linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                           const __grid_constant__ CUtensorMap map_v, ScanParams p, uint32_t* error_word) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* s_wtab = reinterpret_cast<float*>(smem + kOffWtab);
+  float* s_pow = reinterpret_cast<float*>(smem + kOffPow);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  uint64_t* bar_full = bars;              // [3] TMA bytes landed                      (count 1 + tx)
+  uint64_t* bar_stage_free = bars + 3;    // [3] last MMA reading the stage retired    (commit)
+  uint64_t* bar_s_done = bars + 6;        // [2] S_c complete                          (commit)
+  uint64_t* bar_vw_ready = bars + 8;      // [2] Vw_c written                          (128 arrivals)
+  uint64_t* bar_d_done = bars + 10;       // [2] O2_c and M_c complete                 (commit)
+  uint64_t* bar_o1_done = bars + 12;      // [2] O1_c complete                         (commit)
+  uint64_t* bar_acc_free = bars + 14;     // [2] epilogue c has read O1_c, O2_c        (128 arrivals)
+  uint64_t* bar_p_ready = bars + 16;      // [1] P_c written                           (128 arrivals)
+  uint64_t* bar_state_ready = bars + 17;  // [1] bf16 state copy + rescaled TMEM state (128 arrivals)
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 8);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int64_t b = blockIdx.x;
+  const int n_chunks = static_cast<int>(p.T / kChunk);
+
+  // ---- set-up (all threads) ----
+  if (tid == 0) {
+    for (int i = 0; i < 3; ++i) mbar_init(&bar_full[i], 1);
+    for (int i = 0; i < 3; ++i) mbar_init(&bar_stage_free[i], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_s_done[i], 1);
+      mbar_init(&bar_vw_ready[i], 128);
+      mbar_init(&bar_d_done[i], 1);
+      mbar_init(&bar_o1_done[i], 1);
+      mbar_init(&bar_acc_free[i], 128);
+    }
+    mbar_init(bar_p_ready, 128);
+    mbar_init(bar_state_ready, 128);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int j = tid; j <= kChunk; j += kThreads) s_pow[j] = powf(p.decay, static_cast<float>(j));
+  for (int j = tid; j < 256; j += kThreads) {
+    const int d = j - 128;
+    s_wtab[j] = d >= 0 ? p.hidden_scale * p.update_coeff * powf(p.decay, static_cast<float>(d)) : 0.0f;
+  }
+  // P is lower triangular in 32-column blocks: the blocks above the diagonal stay zero forever
+  for (int i = tid; i < 2 * kTileBytes / 16; i += kThreads) {
+    reinterpret_cast<uint4*>(smem + kOffP)[i] = make_uint4(0, 0, 0, 0);
+  }
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  uint8_t* s_p = smem + kOffP;
+  uint8_t* s_mb = smem + kOffMb;
+  auto stage_q = [&](int s) { return smem + kOffStage + s * kStageBytes; };
+  auto stage_k = [&](int s) { return stage_q(s) + kTileBytes; };
+  auto stage_v = [&](int s) { return stage_q(s) + 2 * kTileBytes; };
+  auto vw_buf = [&](int i) { return smem + kOffVw + i * kTileBytes; };
+
+#define GRMX_WAIT(bar, phase)                                        \
+  if (!mbar_wait((bar), static_cast<uint32_t>(phase) & 1u, s_abort)) \
+    break;
+
+  // Protocol.  "phase n of X" = the n-th completion of barrier X.  Each barrier is completed by
+  // one producer event per chunk (or per two/three chunks for the [2]/[3] arrays) and every
+  // waiter needs an event that the producer cannot get more than one phase ahead of, because
+  // the producer's next event itself depends on the waiter's progress:
+  //   S_{c+2} needs acc_free(c)  <- epilogue c      <- o1_done(c)
+  //   M_c, O2_c need vw_ready(c) <- Vw pass c       <- d_done(c-2), full(c)
+  //                  state_ready(c) <- state pass c-1 <- d_done(c-1)
+  //   O1_c needs p_ready(c)      <- P pass c        <- s_done(c), o1_done(c-1)
+  //   TMA c needs stage_free(c-3) <- O1_{c-3}
+
+  if (warp == kTmaWarp) {
+    // ===================================================================== TMA producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int c = 0; c < n_chunks; ++c) {
+        const int s = c % kStages;
+        if (c >= kStages) GRMX_WAIT(&bar_stage_free[s], c / kStages - 1)
+        mbar_expect_tx(&bar_full[s], kStageBytes);
+        const int t0 = c * kChunk;
+        tma_load_3d(stage_q(s), &map_q, &bar_full[s], 0, t0, static_cast<int>(b));
+        tma_load_3d(stage_k(s), &map_k, &bar_full[s], 0, t0, static_cast<int>(b));
+        tma_load_3d(stage_v(s), &map_v, &bar_full[s], 0, t0, static_cast<int>(b));
+        issued = c + 1;
+      }
+      if (*s_abort) {
+        // let the copies still in flight land before the shared memory is released
+        for (int c = issued > kStages ? issued - kStages : 0; c < issued; ++c) {
+          mbar_wait_quiet(&bar_full[c % kStages], (c / kStages) & 1);
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ===================================================================== MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(kChunk, kChunk, 0, 0);
+      constexpr uint32_t idesc_o2 = make_idesc(kChunk, kD, 0, 0);
+      constexpr uint32_t idesc_m = make_idesc(kD, kD, 1, 1);
+      constexpr uint32_t idesc_o1 = make_idesc(kChunk, kD, 0, 1);
+      const uint64_t desc_p = smem_desc(smem_u32(s_p), 16, 1024);
+      const uint64_t desc_mb = smem_desc(smem_u32(s_mb), 16, 1024);
+
+      auto issue_s = [&](int c) {
+        const int s = c % kStages;
+        const uint64_t dq = smem_desc(smem_u32(stage_q(s)), 16, 1024);
+        const uint64_t dk = smem_desc(smem_u32(stage_k(s)), 16, 1024);
+        const uint32_t d_tmem = tmem_base + kColSO + 128u * (c & 1);
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          tc_mma_bf16(d_tmem, desc_add(dq, kk * 32), desc_add(dk, kk * 32), idesc_s, kk > 0);
+        }
+        tc_commit(&bar_s_done[c & 1]);
+      };
+
+      do {
+        GRMX_WAIT(&bar_full[0], 0)
+        tc_fence_after();
+        issue_s(0);
+        for (int c = 0; c < n_chunks; ++c) {
+          const int s = c % kStages;
+          if (c + 1 < n_chunks) {
+            const int n = c + 1;
+            GRMX_WAIT(&bar_full[n % kStages], n / kStages)
+            if (n >= 2) GRMX_WAIT(&bar_acc_free[n & 1], n / 2 - 1)
+            tc_fence_after();
+            issue_s(n);
+          }
+          GRMX_WAIT(&bar_vw_ready[c & 1], c / 2)
+          GRMX_WAIT(bar_state_ready, c)
+          tc_fence_after();
+          {
+            const uint64_t dq = smem_desc(smem_u32(stage_q(s)), 16, 1024);
+            const uint64_t dk_mn = smem_desc(smem_u32(stage_k(s)), kTileBytes, 1024);
+            const uint64_t dvw = smem_desc(smem_u32(vw_buf(c & 1)), kTileBytes, 1024);
+            const uint32_t o2_tmem = tmem_base + kColO2 + 64u * (c & 1);
+#pragma unroll
+            for (int kk = 0; kk < kD / 16; ++kk) {
+              tc_mma_bf16(o2_tmem, desc_add(dq, kk * 32), desc_add(desc_mb, kk * 32), idesc_o2, kk > 0);
+            }
+#pragma unroll
+            for (int kk = 0; kk < kChunk / 16; ++kk) {
+              tc_mma_bf16(tmem_base + kColM, desc_add(dvw, kk * 2048), desc_add(dk_mn, kk * 2048), idesc_m, 1u);
+            }
+            tc_commit(&bar_d_done[c & 1]);
+          }
+          GRMX_WAIT(bar_p_ready, c)
+          tc_fence_after();
+          {
+            const uint64_t dv_mn = smem_desc(smem_u32(stage_v(s)), kTileBytes, 1024);
+            const uint32_t o1_tmem = tmem_base + kColSO + 128u * (c & 1);
+#pragma unroll
+            for (int kk = 0; kk < kChunk / 16; ++kk) {
+              const uint32_t off_p = (kk / 4) * kTileBytes + (kk % 4) * 32;
+              tc_mma_bf16(o1_tmem, desc_add(desc_p, off_p), desc_add(dv_mn, kk * 2048), idesc_o1, kk > 0);
+            }
+            tc_commit(&bar_o1_done[c & 1]);
+            tc_commit(&bar_stage_free[s]);
+          }
+        }
+      } while (false);
+    }
+  } else if (warp < 4) {
+    // ===================================================================== P group
+    const int row = tid;                      // token row within the chunk == TMEM lane
+    const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+
+    auto vw_pass = [&](int c) {
+      const float w = p.update_coeff * s_pow[kChunk - 1 - row];
+      const uint8_t* src = stage_v(c % kStages) + row * 128;
+      uint8_t* dst = vw_buf(c & 1) + row * 128;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int ch = (i + row) & 7;   // rotate so that 8 neighbouring rows hit 8 bank groups
+        uint4 raw = *reinterpret_cast<const uint4*>(src + ch * 16);
+        uint32_t* words = reinterpret_cast<uint32_t*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = __uint_as_float(words[j] << 16) * w;
+          const float hi = __uint_as_float(words[j] & 0xffff0000u) * w;
+          words[j] = pack_bf16(lo, hi);
+        }
+        *reinterpret_cast<uint4*>(dst + ch * 16) = raw;
+      }
+      fence_proxy_async();
+      mbar_arrive(&bar_vw_ready[c & 1]);
+    };
+
+    do {
+      GRMX_WAIT(&bar_full[0], 0)
+      vw_pass(0);
+      for (int c = 0; c < n_chunks; ++c) {
+        GRMX_WAIT(&bar_s_done[c & 1], c / 2)
+        if (c >= 1) GRMX_WAIT(&bar_o1_done[(c - 1) & 1], (c - 1) / 2)
+        tc_fence_after();
+        // S_c -> P_c: 32-column blocks at or below the diagonal only (warp w owns rows 32w..32w+31)
+        const uint32_t s_tmem_row = tmem_lane + kColSO + 128u * (c & 1);
+        for (int blk = 0; blk <= warp; ++blk) {
+          const int c0 = blk * 32;
+          float v[32];
+          tc_ld32(s_tmem_row + c0, v);
+          const float* wt = s_wtab + (row - c0 + 128);      // weight of column c0 + jj is wt[-jj]
+          uint8_t* prow = s_p + (c0 / 64) * kTileBytes + row * 128;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            float x[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = v[ch * 8 + j] * wt[-(ch * 8 + j)];
+            uint4 w;
+            w.x = pack_bf16(x[0], x[1]);
+            w.y = pack_bf16(x[2], x[3]);
+            w.z = pack_bf16(x[4], x[5]);
+            w.w = pack_bf16(x[6], x[7]);
+            const int chunk16 = ((c0 % 64) / 8 + ch) ^ (row & 7);
+            *reinterpret_cast<uint4*>(prow + chunk16 * 16) = w;
+          }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        mbar_arrive(bar_p_ready);
+
+        if (c + 1 < n_chunks) {
+          const int n = c + 1;
+          GRMX_WAIT(&bar_full[n % kStages], n / kStages)
+          if (n >= 2) GRMX_WAIT(&bar_d_done[n & 1], n / 2 - 1)
+          vw_pass(n);
+        }
+      }
+    } while (false);
+  } else {
+    // ===================================================================== E group (warps 4-7)
+    const int quarter = warp - 4;
+    const int row = tid - 128;                // token row within the chunk == TMEM lane
+    const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const bool owns_row = lane < 16;          // M = 64 accumulator: lanes 0-15 of each quarter
+    const int state_row = quarter * 16 + (lane & 15);
+    const float carry = s_pow[kChunk];
+    const float row_scale = p.hidden_scale * s_pow[row + 1];
+
+    auto write_mb = [&](const float (&v)[32], int c0) {
+      uint8_t* mrow = s_mb + state_row * 128;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        const int chunk16 = (c0 / 8 + ch) ^ (state_row & 7);
+        uint4 w;
+        w.x = pack_bf16(v[ch * 8 + 0], v[ch * 8 + 1]);
+        w.y = pack_bf16(v[ch * 8 + 2], v[ch * 8 + 3]);
+        w.z = pack_bf16(v[ch * 8 + 4], v[ch * 8 + 5]);
+        w.w = pack_bf16(v[ch * 8 + 6], v[ch * 8 + 7]);
+        *reinterpret_cast<uint4*>(mrow + chunk16 * 16) = w;
+      }
+    };
+
+    // initial state -> bf16 copy + TMEM (pre-scaled by the first chunk's carry)
+    {
+      const float* m_in = static_cast<const float*>(p.memory_in) + b * kD * kD;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kD; c0 += 32) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          v[j] = owns_row ? m_in[state_row * p.m_row_stride + (c0 + j) * p.m_col_stride] : 0.0f;
+        }
+        if (owns_row) write_mb(v, c0);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= carry;
+        tc_st32(tmem_lane + kColM + c0, v);
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(bar_state_ready);   // phase 0
+    }
+
+    do {
+      for (int c = 0; c < n_chunks; ++c) {
+        const bool last = c + 1 == n_chunks;
+        // ---- state pass: M_c is complete ----
+        GRMX_WAIT(&bar_d_done[c & 1], c / 2)
+        tc_fence_after();
+        float* m_out = p.memory_out != nullptr ? static_cast<float*>(p.memory_out) + b * kD * kD : nullptr;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kD; c0 += 32) {
+          float v[32];
+          tc_ld32(tmem_lane + kColM + c0, v);
+          if (last) {
+            if (owns_row && m_out != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 o;
+                o.x = v[j] * p.memory_out_scale;
+                o.y = v[j + 1] * p.memory_out_scale;
+                o.z = v[j + 2] * p.memory_out_scale;
+                o.w = v[j + 3] * p.memory_out_scale;
+                *reinterpret_cast<float4*>(m_out + state_row * kD + c0 + j) = o;
+              }
+            }
+          } else {
+            if (owns_row) write_mb(v, c0);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= carry;
+            tc_st32(tmem_lane + kColM + c0, v);
+          }
+        }
+        if (!last) {
+          fence_proxy_async();
+          tc_fence_before();
+          mbar_arrive(bar_state_ready);   // phase c + 1
+        }
+        // ---- epilogue: out row = O1 + hidden_scale * decay^(row+1) * O2 ----
+        GRMX_WAIT(&bar_o1_done[c & 1], c / 2)
+        tc_fence_after();
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.hidden_out) +
+                             (b * p.T + static_cast<int64_t>(c) * kChunk + row) * kD;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kD; c0 += 32) {
+          float o1[32], o2[32];
+          tc_ld32(tmem_lane + kColSO + 128u * (c & 1) + c0, o1);
+          tc_ld32(tmem_lane + kColO2 + 64u * (c & 1) + c0, o2);
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            float x[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = fmaf(row_scale, o2[ch * 8 + j], o1[ch * 8 + j]);
+            uint4 w;
+            w.x = pack_bf16(x[0], x[1]);
+            w.y = pack_bf16(x[2], x[3]);
+            w.z = pack_bf16(x[4], x[5]);
+            w.w = pack_bf16(x[6], x[7]);
+            *reinterpret_cast<uint4*>(out + c0 + ch * 8) = w;
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&bar_acc_free[c & 1]);
+      }
+    } while (false);
+  }
+#undef GRMX_WAIT
+
+  // ---- teardown (all threads) ----
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *s_abort && error_word != nullptr) atomicOr(error_word, kErrBoundedWait);
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+}  // namespace
+
+bool scan_tcgen05_pipe_supported(const ScanParams& p) { return p.K == kD && p.H == kD; }
+
+int launch_scan_tcgen05_pipe(const ScanParams& p, cudaStream_t stream) {
+  static std::mutex mutex;
+  static bool configured[64] = {false};
+  int device = 0;
+  cudaGetDevice(&device);
+  cudaError_t attr_status = cudaSuccess;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (device >= 0 && device < 64 && !configured[device]) {
+      attr_status = cudaFuncSetAttribute(linear_scan_tc_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemAlloc);
+      configured[device] = attr_status == cudaSuccess;
+    }
+  }
+  if (attr_status != cudaSuccess) {
+    return fail(GRMX_ERR_LAUNCH, "tcgen05 scan: cannot reserve %d bytes of shared memory: %s", kSmemAlloc,
+                cudaGetErrorString(attr_status));
+  }
+  CUtensorMap map_q, map_k, map_v;
+  if (!make_token_map(&map_q, p.queries, p.B, p.T, kD) || !make_token_map(&map_k, p.keys, p.B, p.T, kD) ||
+      !make_token_map(&map_v, p.values, p.B, p.T, kD)) {
+    return fail(GRMX_ERR_LAUNCH, "tcgen05 scan: cuTensorMapEncodeTiled failed");
+  }
+  linear_scan_tc_pipe_kernel<<<static_cast<unsigned>(p.B), kThreads, kSmemAlloc, stream>>>(
+      map_q, map_k, map_v, p, device_error_word_ptr());
+  return check_launch("linear_scan_tcgen05_pipe");
+}
+
+}  // namespace grmx

@@ -30,4 +30,8 @@ int launch_scan_ffma(const ScanParams& p, int io_dtype, int state_dtype, cudaStr
 bool scan_tcgen05_supported(const ScanParams& p, int io_dtype, int state_dtype, const char** why);
 int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream);
 
+// Warp-specialised variant of the tcgen05 scan (d_k = d_v = 64); same coverage rules otherwise.
+bool scan_tcgen05_pipe_supported(const ScanParams& p);
+int launch_scan_tcgen05_pipe(const ScanParams& p, cudaStream_t stream);
+
 }  // namespace grmx
