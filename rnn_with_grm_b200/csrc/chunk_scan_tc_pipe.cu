@@ -10,7 +10,11 @@
 //   warps 0-3  "P" group:    Vw_{c+1} (scaled copy of Vc) and S_c -> P_c (decay mask, bf16)
 //   warps 4-7  "E" group:    state pass (M_c -> bf16 copy, rescale) and epilogue (O1_c, O2_c -> HBM)
 //
-// TMEM (512 columns): two S/O1 buffers, two O2 buffers, the state.  Every
+// P never touches shared memory: the P group rounds it to bf16 in registers and stores it back
+// into the first 64 TMEM columns of the S buffer it came from (two bf16 per column), and O1 = P Vc
+// takes its A operand straight from TMEM, accumulating into the other 64 columns of that buffer.
+//
+// TMEM (512 columns): two S/P/O1 buffers, two O2 buffers, the state.  Every
 // hand-off is an mbarrier; producers and consumers are never more than one
 // phase apart (see the protocol comment in the kernel), and every wait is
 // bounded: on expiry the CTA-wide abort flag is raised, all roles drain, the
@@ -37,18 +41,22 @@ constexpr int kThreads = 320;
 constexpr int kMmaWarp = 8;
 constexpr int kTmaWarp = 9;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColSO = 0;         // + 128 * buffer : S (128 cols), then O1 (first 64 cols)
+constexpr uint32_t kColSO = 0;         // + 128 * buffer : S (128 cols); then P (cols 0-63, bf16 pairs) | O1 (cols 64-127)
 constexpr uint32_t kColO2 = 256;       // + 64 * buffer
 constexpr uint32_t kColM = 384;        // state: 64 columns, lanes 0-15 of each quarter
 
 constexpr int kTileBytes = kChunk * kD * 2;          // 16 KiB: one [128 x 64] bf16 tile
 constexpr int kStageBytes = 3 * kTileBytes;          // q, k, v
 constexpr int kOffStage = 0;
-constexpr int kOffP = kStages * kStageBytes;         // [128 x 128] bf16 as two K-major blocks
-constexpr int kOffVw = kOffP + 2 * kTileBytes;       // two buffers
+constexpr int kOffVw = kStages * kStageBytes;        // two buffers
 constexpr int kOffMb = kOffVw + 2 * kTileBytes;      // [64 x 64] bf16
-constexpr int kOffWtab = kOffMb + kD * kD * 2;       // float[256]: weight(d), d = i - j in [-128, 127]
-constexpr int kOffPow = kOffWtab + 256 * 4;          // float[kChunk + 4]: decay^j
+// Decay weights of P, reversed (entry m holds weight(d = 127 - m), zero for d < 0) and stored as
+// four copies shifted by 0..3 entries so that any run of 32 weights can be read with aligned
+// 16-byte loads; copies are 264 floats apart, which keeps the eight lanes of a load phase on
+// distinct banks.
+constexpr int kWcopy = 264;
+constexpr int kOffWtab = kOffMb + kD * kD * 2;
+constexpr int kOffPow = kOffWtab + 4 * kWcopy * 4;   // float[kChunk + 4]: decay^j
 constexpr int kOffBars = kOffPow + (kChunk + 4) * 4;
 constexpr int kNumBars = 20;
 constexpr int kOffMisc = kOffBars + kNumBars * 8;
@@ -77,8 +85,8 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   uint64_t* bar_d_done = bars + 10;       // [2] O2_c and M_c complete                 (commit)
   uint64_t* bar_o1_done = bars + 12;      // [2] O1_c complete                         (commit)
   uint64_t* bar_acc_free = bars + 14;     // [2] epilogue c has read O1_c, O2_c        (128 arrivals)
-  uint64_t* bar_p_ready = bars + 16;      // [1] P_c written                           (128 arrivals)
-  uint64_t* bar_state_ready = bars + 17;  // [1] bf16 state copy + rescaled TMEM state (128 arrivals)
+  uint64_t* bar_p_ready = bars + 16;      // [2] P_c written (the P group may run a chunk ahead) (128 arrivals)
+  uint64_t* bar_state_ready = bars + 18;  // [1] bf16 state copy + rescaled TMEM state (128 arrivals)
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 8);
 
@@ -99,19 +107,17 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       mbar_init(&bar_o1_done[i], 1);
       mbar_init(&bar_acc_free[i], 128);
     }
-    mbar_init(bar_p_ready, 128);
+    mbar_init(&bar_p_ready[0], 128);
+    mbar_init(&bar_p_ready[1], 128);
     mbar_init(bar_state_ready, 128);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int j = tid; j <= kChunk; j += kThreads) s_pow[j] = powf(p.decay, static_cast<float>(j));
-  for (int j = tid; j < 256; j += kThreads) {
-    const int d = j - 128;
+  for (int j = tid; j < 4 * kWcopy; j += kThreads) {
+    const int copy = j / kWcopy;
+    const int d = 127 - (j % kWcopy + copy);
     s_wtab[j] = d >= 0 ? p.hidden_scale * p.update_coeff * powf(p.decay, static_cast<float>(d)) : 0.0f;
-  }
-  // P is lower triangular in 32-column blocks: the blocks above the diagonal stay zero forever
-  for (int i = tid; i < 2 * kTileBytes / 16; i += kThreads) {
-    reinterpret_cast<uint4*>(smem + kOffP)[i] = make_uint4(0, 0, 0, 0);
   }
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
@@ -125,7 +131,6 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
 
-  uint8_t* s_p = smem + kOffP;
   uint8_t* s_mb = smem + kOffMb;
   auto stage_q = [&](int s) { return smem + kOffStage + s * kStageBytes; };
   auto stage_k = [&](int s) { return stage_q(s) + kTileBytes; };
@@ -143,7 +148,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   //   S_{c+2} needs acc_free(c)  <- epilogue c      <- o1_done(c)
   //   M_c, O2_c need vw_ready(c) <- Vw pass c       <- d_done(c-2), full(c)
   //                  state_ready(c) <- state pass c-1 <- d_done(c-1)
-  //   O1_c needs p_ready(c)      <- P pass c        <- s_done(c), o1_done(c-1)
+  //   O1_c needs p_ready(c)      <- P pass c        <- s_done(c)
   //   TMA c needs stage_free(c-3) <- O1_{c-3}
 
   if (warp == kTmaWarp) {
@@ -174,7 +179,6 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       constexpr uint32_t idesc_o2 = make_idesc(kChunk, kD, 0, 0);
       constexpr uint32_t idesc_m = make_idesc(kD, kD, 1, 1);
       constexpr uint32_t idesc_o1 = make_idesc(kChunk, kD, 0, 1);
-      const uint64_t desc_p = smem_desc(smem_u32(s_p), 16, 1024);
       const uint64_t desc_mb = smem_desc(smem_u32(s_mb), 16, 1024);
 
       auto issue_s = [&](int c) {
@@ -220,15 +224,15 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             }
             tc_commit(&bar_d_done[c & 1]);
           }
-          GRMX_WAIT(bar_p_ready, c)
+          GRMX_WAIT(&bar_p_ready[c & 1], c / 2)
           tc_fence_after();
           {
             const uint64_t dv_mn = smem_desc(smem_u32(stage_v(s)), kTileBytes, 1024);
-            const uint32_t o1_tmem = tmem_base + kColSO + 128u * (c & 1);
+            const uint32_t p_tmem = tmem_base + kColSO + 128u * (c & 1);   // 16 tokens of P = 8 columns
+            const uint32_t o1_tmem = p_tmem + 64u;
 #pragma unroll
             for (int kk = 0; kk < kChunk / 16; ++kk) {
-              const uint32_t off_p = (kk / 4) * kTileBytes + (kk % 4) * 32;
-              tc_mma_bf16(o1_tmem, desc_add(desc_p, off_p), desc_add(dv_mn, kk * 2048), idesc_o1, kk > 0);
+              tc_mma_bf16_ts(o1_tmem, p_tmem + 8u * kk, desc_add(dv_mn, kk * 2048), idesc_o1, kk > 0);
             }
             tc_commit(&bar_o1_done[c & 1]);
             tc_commit(&bar_stage_free[s]);
@@ -267,33 +271,43 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       vw_pass(0);
       for (int c = 0; c < n_chunks; ++c) {
         GRMX_WAIT(&bar_s_done[c & 1], c / 2)
-        if (c >= 1) GRMX_WAIT(&bar_o1_done[(c - 1) & 1], (c - 1) / 2)
         tc_fence_after();
-        // S_c -> P_c: 32-column blocks at or below the diagonal only (warp w owns rows 32w..32w+31)
-        const uint32_t s_tmem_row = tmem_lane + kColSO + 128u * (c & 1);
-        for (int blk = 0; blk <= warp; ++blk) {
-          const int c0 = blk * 32;
-          float v[32];
-          tc_ld32(s_tmem_row + c0, v);
-          const float* wt = s_wtab + (row - c0 + 128);      // weight of column c0 + jj is wt[-jj]
-          uint8_t* prow = s_p + (c0 / 64) * kTileBytes + row * 128;
+        // S_c -> P_c in place.  Warp w owns rows 32w..32w+31, so 32-column blocks above block w are
+        // all zero.  P block b (16 packed columns) overwrites the S columns 16b..16b+15, which
+        // belong to S blocks 0 and 1: those two are in registers before anything is stored.
+        const uint32_t so_row = tmem_lane + kColSO + 128u * (c & 1);
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            float x[8];
+        for (int half = 0; half < 2; ++half) {
+          uint32_t sv[2][32];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) x[j] = v[ch * 8 + j] * wt[-(ch * 8 + j)];
-            uint4 w;
-            w.x = pack_bf16(x[0], x[1]);
-            w.y = pack_bf16(x[2], x[3]);
-            w.z = pack_bf16(x[4], x[5]);
-            w.w = pack_bf16(x[6], x[7]);
-            const int chunk16 = ((c0 % 64) / 8 + ch) ^ (row & 7);
-            *reinterpret_cast<uint4*>(prow + chunk16 * 16) = w;
+          for (int u = 0; u < 2; ++u) {
+            if (2 * half + u <= warp) tc_ld32_async(so_row + 32u * (2 * half + u), sv[u]);
+          }
+          tc_wait_ld();
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int blk = 2 * half + u;
+            uint32_t pk[16];
+            if (blk <= warp) {
+              const int m0 = 127 - row + 32 * blk;            // reversed-table index of column 32*blk
+              const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
+#pragma unroll
+              for (int t = 0; t < 8; ++t) {
+                const float4 w4 = wv[t];
+                pk[2 * t] = pack_bf16(__uint_as_float(sv[u][4 * t]) * w4.x, __uint_as_float(sv[u][4 * t + 1]) * w4.y);
+                pk[2 * t + 1] =
+                    pack_bf16(__uint_as_float(sv[u][4 * t + 2]) * w4.z, __uint_as_float(sv[u][4 * t + 3]) * w4.w);
+              }
+            } else {
+#pragma unroll
+              for (int t = 0; t < 16; ++t) pk[t] = 0u;
+            }
+            tc_st16_async(so_row + 16u * blk, pk);
           }
         }
-        fence_proxy_async();
+        tc_wait_st();
         tc_fence_before();
-        mbar_arrive(bar_p_ready);
+        mbar_arrive(&bar_p_ready[c & 1]);
 
         if (c + 1 < n_chunks) {
           const int n = c + 1;
@@ -387,22 +401,30 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         tc_fence_after();
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.hidden_out) +
                              (b * p.T + static_cast<int64_t>(c) * kChunk + row) * kD;
-#pragma unroll 1
-        for (int c0 = 0; c0 < kD; c0 += 32) {
-          float o1[32], o2[32];
-          tc_ld32(tmem_lane + kColSO + 128u * (c & 1) + c0, o1);
-          tc_ld32(tmem_lane + kColO2 + 64u * (c & 1) + c0, o2);
+        {
+          uint32_t o1[2][32], o2[2][32];
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            float x[8];
+          for (int h = 0; h < 2; ++h) {
+            tc_ld32_async(tmem_lane + kColSO + 128u * (c & 1) + 64u + 32u * h, o1[h]);
+            tc_ld32_async(tmem_lane + kColO2 + 64u * (c & 1) + 32u * h, o2[h]);
+          }
+          tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 8; ++j) x[j] = fmaf(row_scale, o2[ch * 8 + j], o1[ch * 8 + j]);
-            uint4 w;
-            w.x = pack_bf16(x[0], x[1]);
-            w.y = pack_bf16(x[2], x[3]);
-            w.z = pack_bf16(x[4], x[5]);
-            w.w = pack_bf16(x[6], x[7]);
-            *reinterpret_cast<uint4*>(out + c0 + ch * 8) = w;
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              float x[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                x[j] = fmaf(row_scale, __uint_as_float(o2[h][ch * 8 + j]), __uint_as_float(o1[h][ch * 8 + j]));
+              }
+              uint4 w;
+              w.x = pack_bf16(x[0], x[1]);
+              w.y = pack_bf16(x[2], x[3]);
+              w.z = pack_bf16(x[4], x[5]);
+              w.w = pack_bf16(x[6], x[7]);
+              *reinterpret_cast<uint4*>(out + 32 * h + ch * 8) = w;
+            }
           }
         }
         tc_fence_before();
