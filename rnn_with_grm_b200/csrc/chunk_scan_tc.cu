@@ -470,15 +470,13 @@ bool scan_tcgen05_supported(const ScanParams& p, int io_dtype, int state_dtype, 
     *why = "d_k and d_v must both be 64";
     return false;
   }
-  if (p.T < kChunk || p.T % kChunk != 0) {
-    *why = "T must be a positive multiple of 128";
+  // the pipelined kernel takes any T, either direction; the single-warpgroup one only whole chunks
+  const bool simple = p.T % kChunk == 0 && !p.reverse && !p.first_step_no_decay;
+  if (p.T < 1 || (!simple && !scan_tcgen05_pipe_supported(p))) {
+    *why = "this head size needs T to be a multiple of 128 and a forward scan";
     return false;
   }
-  if (p.reverse || p.first_step_no_decay) {
-    *why = "reverse scans and decay-free first steps run on the fp32 path";
-    return false;
-  }
-  if (p.B > 0x7fffffffLL || p.T > 0x7fffffffLL) {
+  if (p.B > 0x7fffffffLL || p.T > 0x7fff0000LL) {
     *why = "B or T exceeds the tensor-map coordinate range";
     return false;
   }
@@ -512,7 +510,10 @@ static bool prefer_sync_variant() {
 }
 
 int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream) {
-  if (scan_tcgen05_pipe_supported(p) && !prefer_sync_variant()) return launch_scan_tcgen05_pipe(p, stream);
+  const bool simple = p.T % kChunk == 0 && !p.reverse && !p.first_step_no_decay;
+  if (scan_tcgen05_pipe_supported(p) && !(simple && prefer_sync_variant())) {
+    return launch_scan_tcgen05_pipe(p, stream);
+  }
   if (p.K == 64 && p.H == 64) return launch<64, 64>(p, stream);
   return fail(GRMX_ERR_UNSUPPORTED, "tcgen05 scan: no kernel for d_k=%lld d_v=%lld", (long long)p.K,
               (long long)p.H);

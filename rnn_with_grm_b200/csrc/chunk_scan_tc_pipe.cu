@@ -94,7 +94,15 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int64_t b = blockIdx.x;
-  const int n_chunks = static_cast<int>(p.T / kChunk);
+  const int T = static_cast<int>(p.T);
+  const int n_chunks = (T + kChunk - 1) / kChunk;
+  const bool rev = p.reverse != 0;
+  // Chunk c covers processing steps [128c, 128c + len).  Forward, tile row r is step r of the
+  // chunk; in a reverse scan the tile is still loaded in memory order, so row r is step 127 - r
+  // and the tile of a short last chunk starts at a negative token (TMA fills those rows with 0).
+  auto chunk_len = [&](int c) { return min(kChunk, T - c * kChunk); };
+  auto chunk_token0 = [&](int c) { return rev ? T - (c + 1) * kChunk : c * kChunk; };
+  auto first_offset = [&](int c) { return (c == 0 && p.first_step_no_decay) ? 1 : 0; };
 
   // ---- set-up (all threads) ----
   if (tid == 0) {
@@ -116,7 +124,8 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   for (int j = tid; j <= kChunk; j += kThreads) s_pow[j] = powf(p.decay, static_cast<float>(j));
   for (int j = tid; j < 4 * kWcopy; j += kThreads) {
     const int copy = j / kWcopy;
-    const int d = 127 - (j % kWcopy + copy);
+    const int m = j % kWcopy + copy;           // forward: weight(row - col), reverse: weight(col - row)
+    const int d = rev ? m - 127 : 127 - m;
     s_wtab[j] = d >= 0 ? p.hidden_scale * p.update_coeff * powf(p.decay, static_cast<float>(d)) : 0.0f;
   }
   if (warp == kMmaWarp) {
@@ -159,7 +168,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         const int s = c % kStages;
         if (c >= kStages) GRMX_WAIT(&bar_stage_free[s], c / kStages - 1)
         mbar_expect_tx(&bar_full[s], kStageBytes);
-        const int t0 = c * kChunk;
+        const int t0 = chunk_token0(c);
         tma_load_3d(stage_q(s), &map_q, &bar_full[s], 0, t0, static_cast<int>(b));
         tma_load_3d(stage_k(s), &map_k, &bar_full[s], 0, t0, static_cast<int>(b));
         tma_load_3d(stage_v(s), &map_v, &bar_full[s], 0, t0, static_cast<int>(b));
@@ -246,7 +255,9 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
 
     auto vw_pass = [&](int c) {
-      const float w = p.update_coeff * s_pow[kChunk - 1 - row];
+      const int len = chunk_len(c);
+      const int step = rev ? kChunk - 1 - row : row;
+      const float w = step < len ? p.update_coeff * s_pow[len - 1 - step] : 0.0f;
       const uint8_t* src = stage_v(c % kStages) + row * 128;
       uint8_t* dst = vw_buf(c & 1) + row * 128;
 #pragma unroll
@@ -272,8 +283,8 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       for (int c = 0; c < n_chunks; ++c) {
         GRMX_WAIT(&bar_s_done[c & 1], c / 2)
         tc_fence_after();
-        // S_c -> P_c in place.  Warp w owns rows 32w..32w+31, so 32-column blocks above block w are
-        // all zero.  P block b (16 packed columns) overwrites the S columns 16b..16b+15, which
+        // S_c -> P_c in place.  Warp w owns rows 32w..32w+31, so 32-column blocks above block w
+        // (below it in a reverse scan) are all zero.  P block b (16 packed columns) overwrites the S columns 16b..16b+15, which
         // belong to S blocks 0 and 1: those two are in registers before anything is stored.
         const uint32_t so_row = tmem_lane + kColSO + 128u * (c & 1);
 #pragma unroll
@@ -281,14 +292,15 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           uint32_t sv[2][32];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            if (2 * half + u <= warp) tc_ld32_async(so_row + 32u * (2 * half + u), sv[u]);
+            const int blk = 2 * half + u;
+            if (rev ? blk >= warp : blk <= warp) tc_ld32_async(so_row + 32u * blk, sv[u]);
           }
           tc_wait_ld();
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
             const int blk = 2 * half + u;
             uint32_t pk[16];
-            if (blk <= warp) {
+            if (rev ? blk >= warp : blk <= warp) {
               const int m0 = 127 - row + 32 * blk;            // reversed-table index of column 32*blk
               const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
 #pragma unroll
@@ -324,8 +336,9 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const bool owns_row = lane < 16;          // M = 64 accumulator: lanes 0-15 of each quarter
     const int state_row = quarter * 16 + (lane & 15);
-    const float carry = s_pow[kChunk];
-    const float row_scale = p.hidden_scale * s_pow[row + 1];
+    const int step = rev ? kChunk - 1 - row : row;   // processing step of this thread's token row
+    // decay applied to the carried state over chunk c (the state in TMEM is kept pre-scaled by it)
+    auto carry_of = [&](int c) { return s_pow[chunk_len(c) - first_offset(c)]; };
 
     auto write_mb = [&](const float (&v)[32], int c0) {
       uint8_t* mrow = s_mb + state_row * 128;
@@ -352,6 +365,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           v[j] = owns_row ? m_in[state_row * p.m_row_stride + (c0 + j) * p.m_col_stride] : 0.0f;
         }
         if (owns_row) write_mb(v, c0);
+        const float carry = carry_of(0);
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] *= carry;
         tc_st32(tmem_lane + kColM + c0, v);
@@ -386,6 +400,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             }
           } else {
             if (owns_row) write_mb(v, c0);
+            const float carry = carry_of(c + 1);
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= carry;
             tc_st32(tmem_lane + kColM + c0, v);
@@ -399,8 +414,10 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         // ---- epilogue: out row = O1 + hidden_scale * decay^(row+1) * O2 ----
         GRMX_WAIT(&bar_o1_done[c & 1], c / 2)
         tc_fence_after();
+        const bool row_live = step < chunk_len(c);
+        const float row_scale = p.hidden_scale * s_pow[step + 1 - first_offset(c)];
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.hidden_out) +
-                             (b * p.T + static_cast<int64_t>(c) * kChunk + row) * kD;
+                             (b * p.T + static_cast<int64_t>(chunk_token0(c)) + row) * kD;
         {
           uint32_t o1[2][32], o2[2][32];
 #pragma unroll
@@ -423,7 +440,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
               w.y = pack_bf16(x[2], x[3]);
               w.z = pack_bf16(x[4], x[5]);
               w.w = pack_bf16(x[6], x[7]);
-              *reinterpret_cast<uint4*>(out + 32 * h + ch * 8) = w;
+              if (row_live) *reinterpret_cast<uint4*>(out + 32 * h + ch * 8) = w;
             }
           }
         }

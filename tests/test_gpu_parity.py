@@ -369,8 +369,8 @@ def test_tcgen05_scan_is_linear_in_values_and_state():
 
 
 def test_tcgen05_path_refuses_what_it_does_not_cover():
-    k, v, q, m = make_chunk(1, 1, 100, 64, 64)
-    with pytest.raises(cabi.GrmxError, match="multiple of 128"):
+    k, v, q, m = make_chunk(1, 1, 100, 32, 64)
+    with pytest.raises(cabi.GrmxError, match="must both be 64"):
         gx.chunk_scan_fwd(dev(k, torch.bfloat16), dev(v, torch.bfloat16), dev(q, torch.bfloat16), dev(m), 0.97,
                           cabi.PATH_TCGEN05)
     with pytest.raises(cabi.GrmxError, match="bf16"):
@@ -378,3 +378,41 @@ def test_tcgen05_path_refuses_what_it_does_not_cover():
     # auto falls back to the fp32 kernel for the same request
     hidden, _ = gx.chunk_scan_fwd(dev(k), dev(v), dev(q), dev(m), 0.97, cabi.PATH_AUTO)
     close(hidden, go.chunk_update_sequential(k, v, q, m, 0.97)[0], FP32_TOL)
+
+
+@pytest.mark.parametrize("T", [1, 5, 127, 129, 200, 300, 1000])
+def test_tcgen05_scan_ragged_lengths(T):
+    args, (want_h, want_m) = _tc_case(T, 3, T, 0.95, False)
+    hidden, m_out = gx.chunk_scan_fwd(*args, 0.95, cabi.PATH_TCGEN05)
+    close(hidden, want_h, LOWP_TOL)
+    close(m_out, want_m, LOWP_TOL)
+    assert cabi.device_error_word() == 0
+
+
+@pytest.mark.parametrize("T", [128, 333])
+@pytest.mark.parametrize("reverse", [False, True])
+@pytest.mark.parametrize("no_decay_first", [False, True])
+def test_tcgen05_linear_scan_general_form(T, reverse, no_decay_first):
+    k, v, q, m = make_chunk(T + 3, 2, T, 64, 64)
+    tk, tv, tq, tm = dev(k, torch.bfloat16), dev(v, torch.bfloat16), dev(q, torch.bfloat16), dev(m)
+    want_h, want_m = go.linear_scan(host(tk), host(tv), host(tq), m, 0.93, 0.31, hidden_scale=1.7,
+                                    memory_out_scale=0.6, reverse=reverse, first_step_no_decay=no_decay_first)
+    hidden, m_out = gx.linear_scan(tk, tv, tq, tm, 0.93, 0.31, 1.7, 0.6, reverse, no_decay_first, cabi.PATH_TCGEN05)
+    close(hidden, want_h, LOWP_TOL)
+    close(m_out, want_m, LOWP_TOL)
+    m_t = dev(np.ascontiguousarray(m.transpose(0, 2, 1)))
+    hidden_t, m_out_t = gx.linear_scan(tk, tv, tq, m_t, 0.93, 0.31, 1.7, 0.6, reverse, no_decay_first,
+                                       cabi.PATH_TCGEN05, transposed_state=True)
+    assert torch.equal(hidden_t, hidden) and torch.equal(m_out_t, m_out)
+
+
+def test_tcgen05_backward_through_three_scans():
+    k, v, q, m = make_chunk(61, 3, 200, 64, 64)
+    rng = np.random.default_rng(62)
+    gh = rng.standard_normal((3, 200, 64)).astype(np.float32)
+    gm = rng.standard_normal((3, 64, 64)).astype(np.float32)
+    tk, tv, tq, tgh = (dev(a, torch.bfloat16) for a in (k, v, q, gh))
+    want = go.chunk_update_backward(host(tgh), gm, host(tk), host(tv), host(tq), m, 0.97)
+    got = gx.chunk_scan_bwd(tgh, dev(gm), tk, tv, tq, dev(m), 0.97, cabi.PATH_TCGEN05)
+    for a, b in zip(got, want):
+        close(a, b, LOWP_TOL)
