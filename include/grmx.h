@@ -93,6 +93,24 @@ int grmx_chunk_scan_fwd(const void* keys, const void* values, const void* querie
                         int io_dtype, int state_dtype, int path, void* stream);
 
 /*
+ * grmx_chunk_scan_fwd with a caller-provided workspace.  When a call has few batch rows and
+ * many tokens the tensor-core path can cut every row along T into pieces that run on different
+ * SMs; the pieces exchange their local state contributions through `scratch` (device memory,
+ * 16-byte aligned, contents irrelevant on entry, not preserved).
+ * grmx_chunk_scan_scratch_bytes returns the size that cut needs for the given call on the
+ * current device, or 0 when the call would not be cut.  With scratch == NULL or a buffer that
+ * is too small the call behaves exactly like grmx_chunk_scan_fwd.  Results are the same up to
+ * floating-point summation order.  Same reference interface as grmx_chunk_scan_fwd.
+ */
+int64_t grmx_chunk_scan_scratch_bytes(int64_t B, int64_t T, int64_t K, int64_t H, int io_dtype,
+                                      int state_dtype);
+int grmx_chunk_scan_fwd_ws(const void* keys, const void* values, const void* queries,
+                           const void* memory_in, void* hidden_out, void* memory_out,
+                           int64_t B, int64_t T, int64_t K, int64_t H, float decay,
+                           int io_dtype, int state_dtype, int path, void* scratch,
+                           int64_t scratch_bytes, void* stream);
+
+/*
  * Gradients of grmx_chunk_scan_fwd: given grad_hidden [B,T,H] (io_dtype) and
  * grad_memory_out [B,H,K] (state_dtype) writes grad_keys, grad_queries
  * [B,T,K], grad_values [B,T,H] (io_dtype) and grad_memory [B,H,K]

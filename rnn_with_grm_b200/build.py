@@ -36,6 +36,7 @@ CUDA_SOURCES = [
     "chunk_scan_ffma.cu",
     "chunk_scan_tc.cu",
     "chunk_scan_tc_pipe.cu",
+    "chunk_scan_tc_split.cu",
     "apply_query.cu",
     "gather.cu",
     "topk_route.cu",

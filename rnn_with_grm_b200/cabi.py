@@ -42,6 +42,11 @@ SIGNATURES = {
         c_int,
         [c_void_p] * 6 + [c_int64] * 4 + [c_float, c_int, c_int, c_int, c_void_p],
     ),
+    "grmx_chunk_scan_scratch_bytes": (c_int64, [c_int64] * 4 + [c_int, c_int]),
+    "grmx_chunk_scan_fwd_ws": (
+        c_int,
+        [c_void_p] * 6 + [c_int64] * 4 + [c_float, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
+    ),
     "grmx_chunk_scan_bwd": (
         c_int,
         [c_void_p] * 10 + [c_int64] * 4 + [c_float, c_int, c_int, c_int, c_void_p],

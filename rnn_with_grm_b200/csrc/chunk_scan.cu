@@ -63,7 +63,7 @@ int copy_state(const ScanParams& p, int state_dtype, cudaStream_t stream) {
 }
 
 int run_scan(const ScanParams& p, int io_dtype, int state_dtype, int path, cudaStream_t stream,
-             const char* who) {
+             const char* who, void* scratch = nullptr, int64_t scratch_bytes = 0) {
   int rc = validate_scan(p, io_dtype, state_dtype, path, who);
   if (rc != GRMX_OK) return rc;
   if (p.B == 0) return GRMX_OK;
@@ -74,7 +74,12 @@ int run_scan(const ScanParams& p, int io_dtype, int state_dtype, int path, cudaS
   if (path == GRMX_PATH_TCGEN05 && !tc_ok) {
     return fail(GRMX_ERR_UNSUPPORTED, "%s: tcgen05 path unavailable: %s", who, why);
   }
-  if (tc_ok && path != GRMX_PATH_FFMA) return launch_scan_tcgen05(p, stream);
+  if (tc_ok && path != GRMX_PATH_FFMA) {
+    if (scratch != nullptr && scan_tcgen05_split_scratch_bytes(p) > 0) {
+      return launch_scan_tcgen05_split(p, scratch, scratch_bytes, stream);
+    }
+    return launch_scan_tcgen05(p, stream);
+  }
   return launch_scan_ffma(p, io_dtype, state_dtype, stream);
 }
 
@@ -120,6 +125,36 @@ int grmx_chunk_scan_fwd(const void* keys, const void* values, const void* querie
   p.memory_out_scale = 1.0f; p.reverse = 0; p.first_step_no_decay = 0;
   return grmx::run_scan(p, io_dtype, state_dtype, path, static_cast<cudaStream_t>(stream),
                         "grmx_chunk_scan_fwd");
+}
+
+int64_t grmx_chunk_scan_scratch_bytes(int64_t B, int64_t T, int64_t K, int64_t H, int io_dtype,
+                                      int state_dtype) {
+  if (B <= 0 || T <= 0 || K <= 0 || H <= 0) return 0;
+  if (io_dtype != GRMX_BF16 || state_dtype != GRMX_F32) return 0;
+  grmx::ScanParams p = {};
+  p.B = B; p.T = T; p.K = K; p.H = H;
+  return grmx::scan_tcgen05_split_scratch_bytes(p);
+}
+
+int grmx_chunk_scan_fwd_ws(const void* keys, const void* values, const void* queries,
+                           const void* memory_in, void* hidden_out, void* memory_out,
+                           int64_t B, int64_t T, int64_t K, int64_t H, float decay,
+                           int io_dtype, int state_dtype, int path, void* scratch,
+                           int64_t scratch_bytes, void* stream) {
+  if (K <= 0) return grmx::fail(GRMX_ERR_ARG, "grmx_chunk_scan_fwd_ws: K must be positive");
+  if (B > 0 && memory_out == nullptr) {
+    return grmx::fail(GRMX_ERR_ARG, "grmx_chunk_scan_fwd_ws: memory_out is NULL");
+  }
+  if (scratch_bytes < 0) return grmx::fail(GRMX_ERR_ARG, "grmx_chunk_scan_fwd_ws: negative scratch size");
+  grmx::ScanParams p;
+  p.keys = keys; p.values = values; p.queries = queries; p.memory_in = memory_in;
+  p.hidden_out = hidden_out; p.memory_out = memory_out;
+  p.B = B; p.T = T; p.K = K; p.H = H;
+  p.m_row_stride = K; p.m_col_stride = 1;
+  p.decay = decay; p.update_coeff = (1.0f - decay) * (1.0f / sqrtf(static_cast<float>(K)));
+  p.hidden_scale = 1.0f; p.memory_out_scale = 1.0f; p.reverse = 0; p.first_step_no_decay = 0;
+  return grmx::run_scan(p, io_dtype, state_dtype, path, static_cast<cudaStream_t>(stream),
+                        "grmx_chunk_scan_fwd_ws", scratch, scratch_bytes);
 }
 
 int grmx_chunk_scan_bwd(const void* grad_hidden, const void* grad_memory_out,

@@ -72,7 +72,8 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { re
 
 __global__ void __launch_bounds__(kThreads, 1)
 linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                           const __grid_constant__ CUtensorMap map_v, ScanParams p, uint32_t* error_word) {
+                           const __grid_constant__ CUtensorMap map_v, ScanParams p, SplitInfo split,
+                           uint32_t* error_word) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* s_wtab = reinterpret_cast<float*>(smem + kOffWtab);
@@ -93,9 +94,16 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int64_t b = blockIdx.x;
+  // The call may be cut along T into `split.pieces` pieces of `split.chunks_per_piece` chunks, one
+  // CTA per (piece, row), piece-major.  Piece q > 0 starts from the state that the pieces before it
+  // leave behind, rebuilt in its prologue from memory_in and their local contributions in
+  // `split.partials` (written by the piece-state kernel that runs before this one).
+  const int64_t b = blockIdx.x % p.B;
+  const int piece = static_cast<int>(blockIdx.x / p.B);
   const int T = static_cast<int>(p.T);
-  const int n_chunks = (T + kChunk - 1) / kChunk;
+  const int total_chunks = (T + kChunk - 1) / kChunk;
+  const int c_begin = piece * split.chunks_per_piece;
+  const int n_chunks = min(split.chunks_per_piece, total_chunks - c_begin);   // chunks of this CTA
   const bool rev = p.reverse != 0;
   // Chunk c covers processing steps [128c, 128c + len).  Forward, tile row r is step r of the
   // chunk; in a reverse scan the tile is still loaded in memory order, so row r is step 127 - r
@@ -168,7 +176,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         const int s = c % kStages;
         if (c >= kStages) GRMX_WAIT(&bar_stage_free[s], c / kStages - 1)
         mbar_expect_tx(&bar_full[s], kStageBytes);
-        const int t0 = chunk_token0(c);
+        const int t0 = chunk_token0(c_begin + c);
         tma_load_3d(stage_q(s), &map_q, &bar_full[s], 0, t0, static_cast<int>(b));
         tma_load_3d(stage_k(s), &map_k, &bar_full[s], 0, t0, static_cast<int>(b));
         tma_load_3d(stage_v(s), &map_v, &bar_full[s], 0, t0, static_cast<int>(b));
@@ -255,7 +263,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
 
     auto vw_pass = [&](int c) {
-      const int len = chunk_len(c);
+      const int len = chunk_len(c_begin + c);
       const int step = rev ? kChunk - 1 - row : row;
       const float w = step < len ? p.update_coeff * s_pow[len - 1 - step] : 0.0f;
       const uint8_t* src = stage_v(c % kStages) + row * 128;
@@ -338,7 +346,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const int state_row = quarter * 16 + (lane & 15);
     const int step = rev ? kChunk - 1 - row : row;   // processing step of this thread's token row
     // decay applied to the carried state over chunk c (the state in TMEM is kept pre-scaled by it)
-    auto carry_of = [&](int c) { return s_pow[chunk_len(c) - first_offset(c)]; };
+    auto carry_of = [&](int c) { return s_pow[chunk_len(c_begin + c) - first_offset(c_begin + c)]; };
 
     auto write_mb = [&](const float (&v)[32], int c0) {
       uint8_t* mrow = s_mb + state_row * 128;
@@ -357,12 +365,45 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // initial state -> bf16 copy + TMEM (pre-scaled by the first chunk's carry)
     {
       const float* m_in = static_cast<const float*>(p.memory_in) + b * kD * kD;
+      const bool dense = p.m_col_stride == 1;
 #pragma unroll 1
       for (int c0 = 0; c0 < kD; c0 += 32) {
         float v[32];
+        if (owns_row && dense) {
+          const float4* src = reinterpret_cast<const float4*>(m_in + state_row * p.m_row_stride + c0);
+          const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v[j] = owns_row ? m_in[state_row * p.m_row_stride + (c0 + j) * p.m_col_stride] : 0.0f;
+          for (int j = 0; j < 8; ++j) {
+            if (vec) {
+              const float4 x = __ldg(src + j);
+              v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) v[4 * j + e] = m_in[state_row * p.m_row_stride + c0 + 4 * j + e];
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = owns_row ? m_in[state_row * p.m_row_stride + (c0 + j) * p.m_col_stride] : 0.0f;
+          }
+        }
+        // state at the start of this piece: M <- decay^(tokens of piece q - offset) M + partial_q
+        for (int q = 0; q < piece; ++q) {
+          const int q_tokens = min(split.chunks_per_piece * kChunk, T - q * split.chunks_per_piece * kChunk);
+          const float g = powf(p.decay, static_cast<float>(q_tokens - first_offset(q * split.chunks_per_piece)));
+          if (owns_row) {
+            const float4* part = reinterpret_cast<const float4*>(
+                split.partials + ((b * (split.pieces - 1) + q) * kD + state_row) * kD + c0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 x = __ldg(part + j);
+              v[4 * j] = fmaf(g, v[4 * j], x.x);
+              v[4 * j + 1] = fmaf(g, v[4 * j + 1], x.y);
+              v[4 * j + 2] = fmaf(g, v[4 * j + 2], x.z);
+              v[4 * j + 3] = fmaf(g, v[4 * j + 3], x.w);
+            }
+          }
         }
         if (owns_row) write_mb(v, c0);
         const float carry = carry_of(0);
@@ -381,7 +422,9 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         // ---- state pass: M_c is complete ----
         GRMX_WAIT(&bar_d_done[c & 1], c / 2)
         tc_fence_after();
-        float* m_out = p.memory_out != nullptr ? static_cast<float*>(p.memory_out) + b * kD * kD : nullptr;
+        float* m_out = (p.memory_out != nullptr && piece + 1 == split.pieces)
+                           ? static_cast<float*>(p.memory_out) + b * kD * kD
+                           : nullptr;
 #pragma unroll 1
         for (int c0 = 0; c0 < kD; c0 += 32) {
           float v[32];
@@ -414,10 +457,10 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         // ---- epilogue: out row = O1 + hidden_scale * decay^(row+1) * O2 ----
         GRMX_WAIT(&bar_o1_done[c & 1], c / 2)
         tc_fence_after();
-        const bool row_live = step < chunk_len(c);
-        const float row_scale = p.hidden_scale * s_pow[step + 1 - first_offset(c)];
+        const bool row_live = step < chunk_len(c_begin + c);
+        const float row_scale = p.hidden_scale * s_pow[step + 1 - first_offset(c_begin + c)];
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.hidden_out) +
-                             (b * p.T + static_cast<int64_t>(chunk_token0(c)) + row) * kD;
+                             (b * p.T + static_cast<int64_t>(chunk_token0(c_begin + c)) + row) * kD;
         {
           uint32_t o1[2][32], o2[2][32];
 #pragma unroll
@@ -465,7 +508,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
 
 bool scan_tcgen05_pipe_supported(const ScanParams& p) { return p.K == kD && p.H == kD; }
 
-int launch_scan_tcgen05_pipe(const ScanParams& p, cudaStream_t stream) {
+int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaStream_t stream) {
   static std::mutex mutex;
   static bool configured[64] = {false};
   int device = 0;
@@ -488,8 +531,8 @@ int launch_scan_tcgen05_pipe(const ScanParams& p, cudaStream_t stream) {
       !make_token_map(&map_v, p.values, p.B, p.T, kD)) {
     return fail(GRMX_ERR_LAUNCH, "tcgen05 scan: cuTensorMapEncodeTiled failed");
   }
-  linear_scan_tc_pipe_kernel<<<static_cast<unsigned>(p.B), kThreads, kSmemAlloc, stream>>>(
-      map_q, map_k, map_v, p, device_error_word_ptr());
+  linear_scan_tc_pipe_kernel<<<static_cast<unsigned>(p.B * split.pieces), kThreads, kSmemAlloc, stream>>>(
+      map_q, map_k, map_v, p, split, device_error_word_ptr());
   return check_launch("linear_scan_tcgen05_pipe");
 }
 

@@ -1,0 +1,277 @@
+// Cutting a scan along T so that a handful of batch rows still fills the GPU.
+//
+// The scan is linear in its start state, so a row can be cut into pieces that run as
+// separate CTAs once every piece knows the state it starts from.  That state is
+//   M_start(q+1) = decay^(tokens of piece q) * M_start(q) + L_q,
+//   L_q = sum over the tokens j of piece q of coeff * decay^(n_q - 1 - step_j) v_j k_j^T,
+// and L_q depends on k and v of piece q only.  `piece_state_kernel` below computes the
+// L_q of every piece but the last (one CTA per piece and row: TMA-fed tcgen05.mma
+// accumulating Vw^T Kc in TMEM, no rescaling between chunks because the decay of the whole
+// piece is folded into the per-token weights) into a scratch buffer the caller provides; the
+// scan kernel launched after it on the same stream rebuilds each piece's start state from
+// memory_in and those L_q in its prologue.  Stream order is the only synchronisation
+// between the two kernels: no CTA ever waits for another.
+//
+// Cost: k and v of all pieces but the last are read twice (the second time mostly from L2)
+// and their Vw^T Kc products are computed twice.
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "scan.cuh"
+#include "tc_ptx.cuh"
+
+namespace grmx {
+namespace {
+
+using namespace tc;
+
+constexpr int kChunk = 128;
+constexpr int kD = 64;
+constexpr int kStages = 3;
+constexpr int kThreads = 192;          // warps 0-3: Vw passes + final read-out, warp 4: MMA, warp 5: TMA
+constexpr int kMmaWarp = 4;
+constexpr int kTmaWarp = 5;
+constexpr uint32_t kTmemCols = 64;
+constexpr int kTileBytes = kChunk * kD * 2;
+constexpr int kStageBytes = 2 * kTileBytes;          // k, v
+constexpr int kOffVw = kStages * kStageBytes;
+constexpr int kOffBars = kOffVw + 2 * kTileBytes;
+constexpr int kOffMisc = kOffBars + 16 * 8;
+constexpr int kSmemAlloc = kOffMisc + 32 + 1024;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+
+__global__ void __launch_bounds__(kThreads, 1)
+piece_state_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   ScanParams p, SplitInfo split, float* partials, uint32_t* error_word) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
+  uint64_t* bar_full = bars;            // [3]
+  uint64_t* bar_stage_free = bars + 3;  // [3]
+  uint64_t* bar_vw_ready = bars + 6;    // [2] 128 arrivals
+  uint64_t* bar_d_done = bars + 8;      // [2] commit
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 8);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int64_t b = blockIdx.x % p.B;
+  const int piece = static_cast<int>(blockIdx.x / p.B);
+  const int T = static_cast<int>(p.T);
+  const bool rev = p.reverse != 0;
+  const int c_begin = piece * split.chunks_per_piece;
+  const int n_chunks = split.chunks_per_piece;                       // pieces before the last are full
+  const int piece_tokens = min(n_chunks * kChunk, T - c_begin * kChunk);
+  auto chunk_len = [&](int c) { return min(kChunk, T - c * kChunk); };
+  auto chunk_token0 = [&](int c) { return rev ? T - (c + 1) * kChunk : c * kChunk; };
+
+  if (tid == 0) {
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&bar_full[i], 1);
+      mbar_init(&bar_stage_free[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_vw_ready[i], 128);
+      mbar_init(&bar_d_done[i], 1);
+    }
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  auto stage_k = [&](int s) { return smem + s * kStageBytes; };
+  auto stage_v = [&](int s) { return smem + s * kStageBytes + kTileBytes; };
+  auto vw_buf = [&](int i) { return smem + kOffVw + i * kTileBytes; };
+
+#define GRMX_WAIT(bar, phase)                                        \
+  if (!mbar_wait((bar), static_cast<uint32_t>(phase) & 1u, s_abort)) \
+    break;
+
+  if (warp == kTmaWarp) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int c = 0; c < n_chunks; ++c) {
+        const int s = c % kStages;
+        if (c >= kStages) GRMX_WAIT(&bar_stage_free[s], c / kStages - 1)
+        mbar_expect_tx(&bar_full[s], kStageBytes);
+        const int t0 = chunk_token0(c_begin + c);
+        tma_load_3d(stage_k(s), &map_k, &bar_full[s], 0, t0, static_cast<int>(b));
+        tma_load_3d(stage_v(s), &map_v, &bar_full[s], 0, t0, static_cast<int>(b));
+        issued = c + 1;
+      }
+      if (*s_abort) {
+        for (int c = issued > kStages ? issued - kStages : 0; c < issued; ++c) {
+          mbar_wait_quiet(&bar_full[c % kStages], (c / kStages) & 1);
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_m = make_idesc(kD, kD, 1, 1);
+      for (int c = 0; c < n_chunks; ++c) {
+        const int s = c % kStages;
+        GRMX_WAIT(&bar_vw_ready[c & 1], c / 2)
+        tc_fence_after();
+        const uint64_t dk_mn = smem_desc(smem_u32(stage_k(s)), kTileBytes, 1024);
+        const uint64_t dvw = smem_desc(smem_u32(vw_buf(c & 1)), kTileBytes, 1024);
+#pragma unroll
+        for (int kk = 0; kk < kChunk / 16; ++kk) {
+          tc_mma_bf16(tmem_base, desc_add(dvw, kk * 2048), desc_add(dk_mn, kk * 2048), idesc_m,
+                      (c > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&bar_d_done[c & 1]);
+        tc_commit(&bar_stage_free[s]);
+      }
+    }
+  } else {
+    // ---- Vw passes, then the read-out of the accumulated contribution ----
+    const int row = tid;
+    const int step = rev ? kChunk - 1 - row : row;
+    bool ok = true;
+    for (int c = 0; c < n_chunks && ok; ++c) {
+      ok = false;
+      do {
+        GRMX_WAIT(&bar_full[c % kStages], c / kStages)
+        if (c >= 2) GRMX_WAIT(&bar_d_done[c & 1], c / 2 - 1)
+        ok = true;
+      } while (false);
+      if (!ok) break;
+      // weight of this token: every later token of the piece decays it once more
+      const int later = piece_tokens - 1 - (c * kChunk + step);
+      const float w = step < chunk_len(c_begin + c) ? p.update_coeff * powf(p.decay, static_cast<float>(later)) : 0.0f;
+      const uint8_t* src = stage_v(c % kStages) + row * 128;
+      uint8_t* dst = vw_buf(c & 1) + row * 128;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int ch = (i + row) & 7;
+        uint4 raw = *reinterpret_cast<const uint4*>(src + ch * 16);
+        uint32_t* words = reinterpret_cast<uint32_t*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = __uint_as_float(words[j] << 16) * w;
+          const float hi = __uint_as_float(words[j] & 0xffff0000u) * w;
+          words[j] = pack_bf16(lo, hi);
+        }
+        *reinterpret_cast<uint4*>(dst + ch * 16) = raw;
+      }
+      fence_proxy_async();
+      mbar_arrive(&bar_vw_ready[c & 1]);
+    }
+    const int last = n_chunks - 1;
+    if (ok && mbar_wait(&bar_d_done[last & 1], (last / 2) & 1, s_abort)) {
+      tc_fence_after();
+      // M = 64 accumulator: lanes 0-15 of each 32-lane quarter hold rows 16*warp + lane
+      const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+      float* out = partials + ((b * (split.pieces - 1) + piece) * kD + (warp * 16 + (lane & 15))) * kD;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kD; c0 += 32) {
+        float v[32];
+        tc_ld32(tmem_lane + c0, v);
+        if (lane < 16) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            *reinterpret_cast<float4*>(out + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          }
+        }
+      }
+    }
+  }
+#undef GRMX_WAIT
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *s_abort && error_word != nullptr) atomicOr(error_word, kErrBoundedWait);
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+int sm_count_of_current_device() {
+  static int cached[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  if (cached[device] == 0) cudaDeviceGetAttribute(&cached[device], cudaDevAttrMultiProcessorCount, device);
+  return cached[device];
+}
+
+// Pieces per row: the largest power of two that still gives every piece two chunks or more and
+// keeps rows x pieces within one wave of the GPU (one CTA per SM).
+int pick_pieces(const ScanParams& p) {
+  if (!scan_tcgen05_pipe_supported(p)) return 1;
+  const int64_t n_chunks = (p.T + kChunk - 1) / kChunk;
+  const int sms = sm_count_of_current_device();
+  int pieces = 1;
+  while (p.B * pieces * 2 <= sms && n_chunks / (pieces * 2) >= 2) pieces *= 2;
+  return pieces;
+}
+
+}  // namespace
+
+int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p) {
+  const int pieces = pick_pieces(p);
+  if (pieces <= 1) return 0;
+  return p.B * (pieces - 1) * kD * kD * static_cast<int64_t>(sizeof(float));
+}
+
+int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
+  const int64_t n_chunks = (p.T + kChunk - 1) / kChunk;
+  const int pieces = pick_pieces(p);
+  const int64_t need = p.B * (pieces - 1) * kD * kD * static_cast<int64_t>(sizeof(float));
+  if (pieces <= 1 || scratch == nullptr || scratch_bytes < need ||
+      (reinterpret_cast<uintptr_t>(scratch) & 15u) != 0) {
+    return launch_scan_tcgen05_pipe(p, SplitInfo{1, static_cast<int>(n_chunks), nullptr}, stream);
+  }
+  SplitInfo split;
+  split.pieces = pieces;
+  split.chunks_per_piece = static_cast<int>((n_chunks + pieces - 1) / pieces);
+  // every piece must own at least one chunk
+  if (static_cast<int64_t>(split.chunks_per_piece) * (pieces - 1) >= n_chunks) {
+    return launch_scan_tcgen05_pipe(p, SplitInfo{1, static_cast<int>(n_chunks), nullptr}, stream);
+  }
+  split.partials = static_cast<const float*>(scratch);
+
+  static std::mutex mutex;
+  static bool configured[64] = {false};
+  int device = 0;
+  cudaGetDevice(&device);
+  cudaError_t attr_status = cudaSuccess;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (device >= 0 && device < 64 && !configured[device]) {
+      attr_status = cudaFuncSetAttribute(piece_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
+      configured[device] = attr_status == cudaSuccess;
+    }
+  }
+  if (attr_status != cudaSuccess) {
+    return fail(GRMX_ERR_LAUNCH, "piece-state kernel: cannot reserve %d bytes of shared memory: %s", kSmemAlloc,
+                cudaGetErrorString(attr_status));
+  }
+  CUtensorMap map_k, map_v;
+  if (!make_token_map(&map_k, p.keys, p.B, p.T, kD) || !make_token_map(&map_v, p.values, p.B, p.T, kD)) {
+    return fail(GRMX_ERR_LAUNCH, "piece-state kernel: cuTensorMapEncodeTiled failed");
+  }
+  piece_state_kernel<<<static_cast<unsigned>(p.B * (pieces - 1)), kThreads, kSmemAlloc, stream>>>(
+      map_k, map_v, p, split, static_cast<float*>(scratch), device_error_word_ptr());
+  int rc = check_launch("piece_state_kernel");
+  if (rc != GRMX_OK) return rc;
+  return launch_scan_tcgen05_pipe(p, split, stream);
+}
+
+}  // namespace grmx

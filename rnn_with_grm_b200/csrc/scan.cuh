@@ -30,8 +30,20 @@ int launch_scan_ffma(const ScanParams& p, int io_dtype, int state_dtype, cudaStr
 bool scan_tcgen05_supported(const ScanParams& p, int io_dtype, int state_dtype, const char** why);
 int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream);
 
+// How a call is cut along T so that few batch rows still fill the GPU.  pieces == 1 means no cut.
+struct SplitInfo {
+  int pieces;              // CTAs per batch row
+  int chunks_per_piece;    // 128-token chunks handled by each of them
+  const float* partials;   // [B, pieces-1, H, K] fp32: local state contribution of pieces 0..pieces-2
+};
+
 // Warp-specialised variant of the tcgen05 scan (d_k = d_v = 64); same coverage rules otherwise.
 bool scan_tcgen05_pipe_supported(const ScanParams& p);
-int launch_scan_tcgen05_pipe(const ScanParams& p, cudaStream_t stream);
+int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaStream_t stream);
+
+// Cutting along T: bytes of scratch the cut needs for this call (0 when a cut would not help or
+// the shape is not covered), and the launch that runs the piece-state kernel followed by the scan.
+int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p);
+int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
 
 }  // namespace grmx

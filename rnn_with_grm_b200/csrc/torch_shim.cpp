@@ -92,11 +92,17 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> chunk_update_forward_cuda(
   }
   auto hidden = at::empty({B, T, H}, v.options());
   auto memory_out = at::empty_like(m);
-  check_status(grmx_chunk_scan_fwd(k.data_ptr(), v.data_ptr(), q.data_ptr(), m.data_ptr(),
-                                   hidden.data_ptr(), memory_out.data_ptr(), B, T, K, H,
-                                   static_cast<float>(memory_decay), dtype_code(k.scalar_type(), "keys"),
-                                   dtype_code(m.scalar_type(), "memory"), g_scan_path.load(),
-                                   current_stream()));
+  const int io = dtype_code(k.scalar_type(), "keys");
+  const int st = dtype_code(m.scalar_type(), "memory");
+  // few rows, many tokens: give the kernel a workspace so it can cut the rows along T
+  const int64_t scratch_bytes = g_scan_path.load() == GRMX_PATH_FFMA ? 0 : grmx_chunk_scan_scratch_bytes(B, T, K, H, io, st);
+  at::Tensor scratch;
+  if (scratch_bytes > 0) scratch = at::empty({scratch_bytes}, k.options().dtype(at::kByte));
+  check_status(grmx_chunk_scan_fwd_ws(k.data_ptr(), v.data_ptr(), q.data_ptr(), m.data_ptr(),
+                                      hidden.data_ptr(), memory_out.data_ptr(), B, T, K, H,
+                                      static_cast<float>(memory_decay), io, st, g_scan_path.load(),
+                                      scratch_bytes > 0 ? scratch.data_ptr() : nullptr, scratch_bytes,
+                                      current_stream()));
   return {hidden, memory_out, aux};
 }
 

@@ -27,6 +27,26 @@ def chunk_scan_fwd(keys, values, queries, memory, decay, path=cabi.PATH_AUTO):
     return hidden, memory_out
 
 
+def chunk_scan_scratch_bytes(B, T, K, H, io_dtype, state_dtype):
+    return int(cabi.load().grmx_chunk_scan_scratch_bytes(B, T, K, H, cabi.dtype_code(io_dtype),
+                                                         cabi.dtype_code(state_dtype)))
+
+
+def chunk_scan_fwd_ws(keys, values, queries, memory, decay, scratch, path=cabi.PATH_AUTO):
+    """Forward scan with a caller-provided workspace (a uint8 CUDA tensor, or None)."""
+    lib = cabi.load()
+    B, T, K = keys.shape
+    H = values.shape[2]
+    hidden = torch.empty(B, T, H, device=keys.device, dtype=values.dtype)
+    memory_out = torch.empty_like(memory)
+    cabi.check(lib.grmx_chunk_scan_fwd_ws(
+        cabi.ptr(keys), cabi.ptr(values), cabi.ptr(queries), cabi.ptr(memory), cabi.ptr(hidden),
+        cabi.ptr(memory_out), B, T, K, H, float(decay), cabi.dtype_code(keys.dtype),
+        cabi.dtype_code(memory.dtype), path, cabi.ptr(scratch), 0 if scratch is None else scratch.numel(),
+        cabi.current_stream()))
+    return hidden, memory_out
+
+
 def chunk_scan_bwd(grad_hidden, grad_memory_out, keys, values, queries, memory, decay, path=cabi.PATH_AUTO):
     lib = cabi.load()
     B, T, K = keys.shape
