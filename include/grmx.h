@@ -111,6 +111,26 @@ int grmx_chunk_scan_fwd_ws(const void* keys, const void* values, const void* que
                            int64_t scratch_bytes, void* stream);
 
 /*
+ * The same scan for callers that cannot allocate device memory where they call it (a server
+ * that has given all of HBM to its own pool, a real-time callback, a sandboxed plugin that
+ * only owns its input and output buffers).  bf16 tokens, fp32 state, d_k = d_v = 64, layouts
+ * as in grmx_chunk_scan_fwd.  The workspace is an array inside the library image,
+ * grmx_static_scratch_capacity() bytes (4 MiB) of device memory held by every GPU that loads
+ * the library until the process exits; a call that would need more is refused with
+ * GRMX_ERR_UNSUPPORTED, and nothing is ever allocated or freed.  The first call on each device
+ * looks the array's address up (cudaGetSymbolAddress, with that device current), so make that
+ * first call outside any stream capture.  All calls share the one array: nothing in it has to
+ * be cleared between calls (each call overwrites what it later reads), but two calls that run
+ * on the GPU at the same time -- different streams, or different host threads -- race on it.
+ * No counterpart in the reference.
+ */
+int64_t grmx_static_scratch_capacity(void);
+int grmx_chunk_scan_fwd_static(const void* keys, const void* values, const void* queries,
+                               const void* memory_in, void* hidden_out, void* memory_out,
+                               int64_t B, int64_t T, int64_t K, int64_t H, float decay,
+                               void* stream);
+
+/*
  * Gradients of grmx_chunk_scan_fwd: given grad_hidden [B,T,H] (io_dtype) and
  * grad_memory_out [B,H,K] (state_dtype) writes grad_keys, grad_queries
  * [B,T,K], grad_values [B,T,H] (io_dtype) and grad_memory [B,H,K]

@@ -17,6 +17,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cmath>
 #include <mutex>
 
 #include "scan.cuh"
@@ -275,3 +276,84 @@ int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratc
 }
 
 }  // namespace grmx
+
+// ---------------------------------------------------------------------------------------
+// Entry point for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc on the path that runs the scan: a serving
+// loop that has handed all of the device memory to its own pool, code running inside a
+// real-time callback where an allocation may block on the driver, or a plugin sandbox that is
+// only given the buffers of its inputs and outputs.  For them the workspace of the T-cut scan
+// lives in the library image instead: a fixed array in device memory, reserved on every GPU
+// that loads the library for as long as the process lives.
+namespace grmx {
+namespace {
+
+constexpr int64_t kStaticScratchBytes = 4ll << 20;   // 4 MiB = 256 piece states of 64 x 64 fp32
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+// Device address of the array on the current device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use, so the address is asked for once
+// per device (with that device current) and remembered.
+int static_scratch_address(float** out) {
+  static std::mutex mutex;
+  static float* cached[64] = {nullptr};
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess || device < 0 || device >= 64) {
+    return fail(GRMX_ERR_DEVICE, "grmx_chunk_scan_fwd_static: no usable current device");
+  }
+  std::lock_guard<std::mutex> lock(mutex);
+  if (cached[device] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return fail(GRMX_ERR_DEVICE, "grmx_chunk_scan_fwd_static: cudaGetSymbolAddress failed: %s",
+                  cudaGetErrorString(err));
+    }
+    cached[device] = static_cast<float*>(ptr);
+  }
+  *out = cached[device];
+  return GRMX_OK;
+}
+
+}  // namespace
+}  // namespace grmx
+
+extern "C" int64_t grmx_static_scratch_capacity(void) { return grmx::kStaticScratchBytes; }
+
+extern "C" int grmx_chunk_scan_fwd_static(const void* keys, const void* values, const void* queries,
+                                          const void* memory_in, void* hidden_out, void* memory_out,
+                                          int64_t B, int64_t T, int64_t K, int64_t H, float decay,
+                                          void* stream) {
+  using namespace grmx;
+  const char* who = "grmx_chunk_scan_fwd_static";
+  GRMX_REQUIRE(B >= 0 && T >= 0 && K > 0 && H > 0, "%s: bad sizes", who);
+  if (B == 0) return GRMX_OK;
+  GRMX_REQUIRE(T > 0, "%s: T must be positive", who);
+  GRMX_REQUIRE(keys && values && queries && memory_in && hidden_out && memory_out, "%s: NULL tensor pointer", who);
+  ScanParams p;
+  p.keys = keys; p.values = values; p.queries = queries; p.memory_in = memory_in;
+  p.hidden_out = hidden_out; p.memory_out = memory_out;
+  p.B = B; p.T = T; p.K = K; p.H = H;
+  p.m_row_stride = K; p.m_col_stride = 1;
+  p.decay = decay; p.update_coeff = (1.0f - decay) * (1.0f / sqrtf(static_cast<float>(K)));
+  p.hidden_scale = 1.0f; p.memory_out_scale = 1.0f; p.reverse = 0; p.first_step_no_decay = 0;
+  const char* why = "";
+  if (!scan_tcgen05_supported(p, GRMX_BF16, GRMX_F32, &why)) {
+    return fail(GRMX_ERR_UNSUPPORTED, "%s: only the bf16 tensor-core scan is offered here: %s", who, why);
+  }
+  const int64_t need = scan_tcgen05_split_scratch_bytes(p);
+  if (need > kStaticScratchBytes) {
+    return fail(GRMX_ERR_UNSUPPORTED,
+                "%s: this call needs %lld bytes of workspace, the built-in one holds %lld; use "
+                "grmx_chunk_scan_fwd_ws with a buffer of your own or fewer rows per call",
+                who, (long long)need, (long long)kStaticScratchBytes);
+  }
+  float* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != GRMX_OK) return rc;
+  return launch_scan_tcgen05_split(p, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+}
+
