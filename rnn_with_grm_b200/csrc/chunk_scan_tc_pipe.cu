@@ -1,27 +1,31 @@
 // Warp-specialised, pipelined tcgen05 kernel of the linear-memory scan
 // (d_k = d_v = 64, bf16 operands, fp32 state in TMEM, chunks of 128 tokens).
 //
-// Same four products per chunk as the synchronous kernel in chunk_scan_tc.cu
-//   S = Q Kc^T,  O2 = Q Mb^T,  M += Vw^T Kc,  O1 = P Vc
-// but the roles run concurrently and only the tiny state hand-off is serial:
+// Per chunk c, with Q, Kc, Vc the chunk's [128 x 64] tiles and M the carried state:
 //
-//   warp 9     TMA producer: q/k/v tiles of chunk c into a 3-stage ring
-//   warp 8     MMA issuer:   S_{c+1} | O2_c, M_c | O1_c  (one thread, tcgen05.mma)
-//   warps 0-3  "P" group:    Vw_{c+1} (scaled copy of Vc) and S_c -> P_c (decay mask, bf16)
-//   warps 4-7  "E" group:    state pass (M_c -> bf16 copy, rescale) and epilogue (O1_c, O2_c -> HBM)
+//   S  = Q Kc^T                                   128 x 128 x 64   smem x smem
+//   O  = Qs Mb^T           Qs_i = hs * decay^(i+1) q_i,  Mb = bf16(M_{c-1})
+//   M  = decay^len M + Vw^T Kc       Vw_j = coeff * decay^(len-1-j) v_j        (state, TMEM)
+//   O += P Vc              P_ij = hs * coeff * decay^(i-j) S_ij (j <= i)       TMEM x smem
+//   out = O
 //
-// P never touches shared memory: the P group rounds it to bf16 in registers and stores it back
-// into the first 64 TMEM columns of the S buffer it came from (two bf16 per column), and O1 = P Vc
-// takes its A operand straight from TMEM, accumulating into the other 64 columns of that buffer.
+// which is the closed form of the reference chunk (grm/core/cuda_ops.py:218-254) with the state
+// carried across chunks as in grm/csrc/grm_cuda.cpp:67-83.  Roles:
 //
-// TMEM (512 columns): two S/P/O1 buffers, two O2 buffers, the state.  Every
-// hand-off is an mbarrier; producers and consumers are never more than one
-// phase apart (see the protocol comment in the kernel), and every wait is
-// bounded: on expiry the CTA-wide abort flag is raised, all roles drain, the
-// error word gets bit 1, TMEM is freed and the kernel returns.
+//   warp 11      TMA producer: q/k/v tiles into a 3-stage ring
+//   warp 10      MMA issuer (one thread): O_c(state part), M_c | O_c(P part) | S_{c+2}
+//   warps 8-9    copy group: Vw_c and Qs_c, the two decay-scaled copies, ahead of the issuer
+//   warps 0-3    compute group 0, chunks 0, 2, 4, ...
+//   warps 4-7    compute group 1, chunks 1, 3, 5, ...
+//                each: S_c -> P_c (decay mask, bf16, written back into the TMEM columns of S_c),
+//                      state pass (M_c -> bf16 copy for the next chunk, rescale in TMEM),
+//                      epilogue (O_c -> bf16 -> HBM)
 //
-// Math: closed form of the reference chunk (grm/core/cuda_ops.py:218-254),
-// state carried across chunks as in grm/csrc/grm_cuda.cpp:67-83.
+// P never touches shared memory: O += P Vc takes its A operand from TMEM.  TMEM (512 columns):
+// two S/P buffers (one per compute group), two O buffers, the state.  Every hand-off is an
+// mbarrier; a waiter is never more than one phase behind its producer (protocol comment in the
+// kernel) and every wait is bounded: on expiry the CTA-wide abort flag is raised, all roles drain,
+// the error word gets bit 1, TMEM is freed and the kernel returns.
 #include <cuda.h>
 
 #include <mutex>
@@ -37,19 +41,22 @@ using namespace tc;
 constexpr int kChunk = 128;
 constexpr int kD = 64;                 // d_k == d_v
 constexpr int kStages = 3;
-constexpr int kThreads = 320;
-constexpr int kMmaWarp = 8;
-constexpr int kTmaWarp = 9;
+constexpr int kThreads = 384;          // 12 warps: 168 registers per thread, no spills
+constexpr int kCopyWarp0 = 8;          // warps 8-9, two token rows per thread
+constexpr int kCopyThreads = 64;
+constexpr int kMmaWarp = 10;
+constexpr int kTmaWarp = 11;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColSO = 0;         // + 128 * buffer : S (128 cols); then P (cols 0-63, bf16 pairs) | O1 (cols 64-127)
-constexpr uint32_t kColO2 = 256;       // + 64 * buffer
+constexpr uint32_t kColS = 0;          // + 128 * group : S (128 cols), then P in cols 0-63 (bf16 pairs)
+constexpr uint32_t kColO = 256;        // + 64 * group  : O
 constexpr uint32_t kColM = 384;        // state: 64 columns, lanes 0-15 of each quarter
 
 constexpr int kTileBytes = kChunk * kD * 2;          // 16 KiB: one [128 x 64] bf16 tile
 constexpr int kStageBytes = 3 * kTileBytes;          // q, k, v
 constexpr int kOffStage = 0;
 constexpr int kOffVw = kStages * kStageBytes;        // two buffers
-constexpr int kOffMb = kOffVw + 2 * kTileBytes;      // [64 x 64] bf16
+constexpr int kOffQs = kOffVw + 2 * kTileBytes;      // two buffers
+constexpr int kOffMb = kOffQs + 2 * kTileBytes;      // [64 x 64] bf16
 // Decay weights of P, reversed (entry m holds weight(d = 127 - m), zero for d < 0) and stored as
 // four copies shifted by 0..3 entries so that any run of 32 weights can be read with aligned
 // 16-byte loads; copies are 264 floats apart, which keeps the eight lanes of a load phase on
@@ -58,10 +65,11 @@ constexpr int kWcopy = 264;
 constexpr int kOffWtab = kOffMb + kD * kD * 2;
 constexpr int kOffPow = kOffWtab + 4 * kWcopy * 4;   // float[kChunk + 4]: decay^j
 constexpr int kOffBars = kOffPow + (kChunk + 4) * 4;
-constexpr int kNumBars = 20;
+constexpr int kNumBars = 24;
 constexpr int kOffMisc = kOffBars + kNumBars * 8;
 constexpr int kSmemTotal = kOffMisc + 32;
 constexpr int kSmemAlloc = kSmemTotal + 1024;
+static_assert(kSmemAlloc <= 232448, "shared memory plan exceeds 227 KiB");
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -69,6 +77,27 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 
 // descriptor + byte offset (the start-address field holds addr >> 4 in its low 14 bits)
 __device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+
+// One token row (128 bytes, 64 bf16) of a swizzled tile times a scalar, into another tile at the
+// same position.  The product is formed by the packed bf16 multiplier (exact product, one
+// rounding), with the scalar itself rounded to bf16 first: the copy is one instruction per two
+// elements, which matters because these copies are the largest block of plain instructions in
+// the kernel.  The 16-byte pieces of a row are visited in an order rotated by the row index so
+// that eight neighbouring rows touch eight different bank groups.
+__device__ __forceinline__ void scaled_row_copy(const uint8_t* src_tile, uint8_t* dst_tile, int row, float w) {
+  const uint8_t* src = src_tile + row * 128;
+  uint8_t* dst = dst_tile + row * 128;
+  const __nv_bfloat162 w2 = __float2bfloat162_rn(w);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int ch = (i + row) & 7;
+    uint4 raw = *reinterpret_cast<const uint4*>(src + ch * 16);
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pairs[j] = __hmul2(pairs[j], w2);
+    *reinterpret_cast<uint4*>(dst + ch * 16) = raw;
+  }
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -79,15 +108,15 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   float* s_wtab = reinterpret_cast<float*>(smem + kOffWtab);
   float* s_pow = reinterpret_cast<float*>(smem + kOffPow);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
-  uint64_t* bar_full = bars;              // [3] TMA bytes landed                      (count 1 + tx)
-  uint64_t* bar_stage_free = bars + 3;    // [3] last MMA reading the stage retired    (commit)
-  uint64_t* bar_s_done = bars + 6;        // [2] S_c complete                          (commit)
-  uint64_t* bar_vw_ready = bars + 8;      // [2] Vw_c written                          (128 arrivals)
-  uint64_t* bar_d_done = bars + 10;       // [2] O2_c and M_c complete                 (commit)
-  uint64_t* bar_o1_done = bars + 12;      // [2] O1_c complete                         (commit)
-  uint64_t* bar_acc_free = bars + 14;     // [2] epilogue c has read O1_c, O2_c        (128 arrivals)
-  uint64_t* bar_p_ready = bars + 16;      // [2] P_c written (the P group may run a chunk ahead) (128 arrivals)
-  uint64_t* bar_state_ready = bars + 18;  // [1] bf16 state copy + rescaled TMEM state (128 arrivals)
+  uint64_t* bar_full = bars;              // [3] TMA bytes landed                             (1 + tx)
+  uint64_t* bar_stage_free = bars + 3;    // [3] last MMA reading the stage retired           (commit)
+  uint64_t* bar_s_done = bars + 6;        // [2] S_c complete                                 (commit)
+  uint64_t* bar_p_ready = bars + 8;       // [2] P_c in TMEM                                  (128)
+  uint64_t* bar_vq_ready = bars + 10;     // [2] Vw_c and Qs_c written                        (64)
+  uint64_t* bar_d_done = bars + 12;       // [2] state part of O_c and M_c complete           (commit)
+  uint64_t* bar_o_done = bars + 14;       // [2] O_c complete                                 (commit)
+  uint64_t* bar_o_free = bars + 16;       // [2] epilogue c has read O_c                      (128)
+  uint64_t* bar_state_ready = bars + 18;  // [1] bf16 state copy + rescaled TMEM state        (128)
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 8);
 
@@ -105,26 +134,27 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const int c_begin = piece * split.chunks_per_piece;
   const int n_chunks = min(split.chunks_per_piece, total_chunks - c_begin);   // chunks of this CTA
   const bool rev = p.reverse != 0;
-  // Chunk c covers processing steps [128c, 128c + len).  Forward, tile row r is step r of the
-  // chunk; in a reverse scan the tile is still loaded in memory order, so row r is step 127 - r
-  // and the tile of a short last chunk starts at a negative token (TMA fills those rows with 0).
-  auto chunk_len = [&](int c) { return min(kChunk, T - c * kChunk); };
-  auto chunk_token0 = [&](int c) { return rev ? T - (c + 1) * kChunk : c * kChunk; };
-  auto first_offset = [&](int c) { return (c == 0 && p.first_step_no_decay) ? 1 : 0; };
+  // Global chunk g covers processing steps [128g, 128g + len).  Forward, tile row r is step r of
+  // the chunk; in a reverse scan the tile is still loaded in memory order, so row r is step
+  // 127 - r and the tile of a short last chunk starts at a negative token (TMA fills with 0).
+  auto chunk_len = [&](int g) { return min(kChunk, T - g * kChunk); };
+  auto chunk_token0 = [&](int g) { return rev ? T - (g + 1) * kChunk : g * kChunk; };
+  auto first_offset = [&](int g) { return (g == 0 && p.first_step_no_decay) ? 1 : 0; };
 
   // ---- set-up (all threads) ----
   if (tid == 0) {
-    for (int i = 0; i < 3; ++i) mbar_init(&bar_full[i], 1);
-    for (int i = 0; i < 3; ++i) mbar_init(&bar_stage_free[i], 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&bar_full[i], 1);
+      mbar_init(&bar_stage_free[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_s_done[i], 1);
-      mbar_init(&bar_vw_ready[i], 128);
+      mbar_init(&bar_p_ready[i], 128);
+      mbar_init(&bar_vq_ready[i], kCopyThreads);
       mbar_init(&bar_d_done[i], 1);
-      mbar_init(&bar_o1_done[i], 1);
-      mbar_init(&bar_acc_free[i], 128);
+      mbar_init(&bar_o_done[i], 1);
+      mbar_init(&bar_o_free[i], 128);
     }
-    mbar_init(&bar_p_ready[0], 128);
-    mbar_init(&bar_p_ready[1], 128);
     mbar_init(bar_state_ready, 128);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -153,20 +183,22 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   auto stage_k = [&](int s) { return stage_q(s) + kTileBytes; };
   auto stage_v = [&](int s) { return stage_q(s) + 2 * kTileBytes; };
   auto vw_buf = [&](int i) { return smem + kOffVw + i * kTileBytes; };
+  auto qs_buf = [&](int i) { return smem + kOffQs + i * kTileBytes; };
 
 #define GRMX_WAIT(bar, phase)                                        \
   if (!mbar_wait((bar), static_cast<uint32_t>(phase) & 1u, s_abort)) \
     break;
 
-  // Protocol.  "phase n of X" = the n-th completion of barrier X.  Each barrier is completed by
-  // one producer event per chunk (or per two/three chunks for the [2]/[3] arrays) and every
-  // waiter needs an event that the producer cannot get more than one phase ahead of, because
-  // the producer's next event itself depends on the waiter's progress:
-  //   S_{c+2} needs acc_free(c)  <- epilogue c      <- o1_done(c)
-  //   M_c, O2_c need vw_ready(c) <- Vw pass c       <- d_done(c-2), full(c)
-  //                  state_ready(c) <- state pass c-1 <- d_done(c-1)
-  //   O1_c needs p_ready(c)      <- P pass c        <- s_done(c)
-  //   TMA c needs stage_free(c-3) <- O1_{c-3}
+  // Protocol.  Chunks are numbered locally, c = 0 .. n_chunks-1; "X(c)" is the completion of
+  // barrier X that belongs to chunk c (phase c/2 of X[c&1], phase c/3 of X[c%3]).  A waiter is
+  // never more than one completion behind, because the producer's next completion on the same
+  // barrier needs something that comes after the waiter's wait:
+  //   issuer:  O_c(state part), M_c  need vq_ready(c)    <- copy group     <- full(c), d_done(c-2)
+  //                                       state_ready(c) <- state pass c-1 <- d_done(c-1)
+  //                                       o_free(c-2)    <- epilogue c-2   <- o_done(c-2)
+  //            O_c(P part)           needs p_ready(c)    <- P pass c       <- s_done(c)
+  //            S_{c+2}               needs o_done(c) (O_c reads its S/P buffer) and full(c+2)
+  //   TMA:     chunk c               needs stage_free(c-3) <- O_{c-3}
 
   if (warp == kTmaWarp) {
     // ===================================================================== TMA producer
@@ -193,16 +225,16 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // ===================================================================== MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(kChunk, kChunk, 0, 0);
-      constexpr uint32_t idesc_o2 = make_idesc(kChunk, kD, 0, 0);
+      constexpr uint32_t idesc_oq = make_idesc(kChunk, kD, 0, 0);
       constexpr uint32_t idesc_m = make_idesc(kD, kD, 1, 1);
-      constexpr uint32_t idesc_o1 = make_idesc(kChunk, kD, 0, 1);
+      constexpr uint32_t idesc_op = make_idesc(kChunk, kD, 0, 1);
       const uint64_t desc_mb = smem_desc(smem_u32(s_mb), 16, 1024);
 
       auto issue_s = [&](int c) {
         const int s = c % kStages;
         const uint64_t dq = smem_desc(smem_u32(stage_q(s)), 16, 1024);
         const uint64_t dk = smem_desc(smem_u32(stage_k(s)), 16, 1024);
-        const uint32_t d_tmem = tmem_base + kColSO + 128u * (c & 1);
+        const uint32_t d_tmem = tmem_base + kColS + 128u * (c & 1);
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
           tc_mma_bf16(d_tmem, desc_add(dq, kk * 32), desc_add(dk, kk * 32), idesc_s, kk > 0);
@@ -214,137 +246,87 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         GRMX_WAIT(&bar_full[0], 0)
         tc_fence_after();
         issue_s(0);
+        if (n_chunks > 1) {
+          GRMX_WAIT(&bar_full[1], 0)
+          tc_fence_after();
+          issue_s(1);
+        }
         for (int c = 0; c < n_chunks; ++c) {
           const int s = c % kStages;
-          if (c + 1 < n_chunks) {
-            const int n = c + 1;
-            GRMX_WAIT(&bar_full[n % kStages], n / kStages)
-            if (n >= 2) GRMX_WAIT(&bar_acc_free[n & 1], n / 2 - 1)
-            tc_fence_after();
-            issue_s(n);
-          }
-          GRMX_WAIT(&bar_vw_ready[c & 1], c / 2)
+          const int g = c & 1;
+          GRMX_WAIT(&bar_vq_ready[g], c / 2)
           GRMX_WAIT(bar_state_ready, c)
+          if (c >= 2) GRMX_WAIT(&bar_o_free[g], c / 2 - 1)
           tc_fence_after();
+          const uint32_t o_tmem = tmem_base + kColO + 64u * g;
           {
-            const uint64_t dq = smem_desc(smem_u32(stage_q(s)), 16, 1024);
+            const uint64_t dqs = smem_desc(smem_u32(qs_buf(g)), 16, 1024);
             const uint64_t dk_mn = smem_desc(smem_u32(stage_k(s)), kTileBytes, 1024);
-            const uint64_t dvw = smem_desc(smem_u32(vw_buf(c & 1)), kTileBytes, 1024);
-            const uint32_t o2_tmem = tmem_base + kColO2 + 64u * (c & 1);
+            const uint64_t dvw = smem_desc(smem_u32(vw_buf(g)), kTileBytes, 1024);
 #pragma unroll
             for (int kk = 0; kk < kD / 16; ++kk) {
-              tc_mma_bf16(o2_tmem, desc_add(dq, kk * 32), desc_add(desc_mb, kk * 32), idesc_o2, kk > 0);
+              tc_mma_bf16(o_tmem, desc_add(dqs, kk * 32), desc_add(desc_mb, kk * 32), idesc_oq, kk > 0);
             }
 #pragma unroll
             for (int kk = 0; kk < kChunk / 16; ++kk) {
               tc_mma_bf16(tmem_base + kColM, desc_add(dvw, kk * 2048), desc_add(dk_mn, kk * 2048), idesc_m, 1u);
             }
-            tc_commit(&bar_d_done[c & 1]);
+            tc_commit(&bar_d_done[g]);
           }
-          GRMX_WAIT(&bar_p_ready[c & 1], c / 2)
+          GRMX_WAIT(&bar_p_ready[g], c / 2)
           tc_fence_after();
           {
             const uint64_t dv_mn = smem_desc(smem_u32(stage_v(s)), kTileBytes, 1024);
-            const uint32_t p_tmem = tmem_base + kColSO + 128u * (c & 1);   // 16 tokens of P = 8 columns
-            const uint32_t o1_tmem = p_tmem + 64u;
+            const uint32_t p_tmem = tmem_base + kColS + 128u * g;   // 16 tokens of P = 8 columns
 #pragma unroll
             for (int kk = 0; kk < kChunk / 16; ++kk) {
-              tc_mma_bf16_ts(o1_tmem, p_tmem + 8u * kk, desc_add(dv_mn, kk * 2048), idesc_o1, kk > 0);
+              tc_mma_bf16_ts(o_tmem, p_tmem + 8u * kk, desc_add(dv_mn, kk * 2048), idesc_op, 1u);
             }
-            tc_commit(&bar_o1_done[c & 1]);
+            tc_commit(&bar_o_done[g]);
             tc_commit(&bar_stage_free[s]);
+          }
+          if (c + 2 < n_chunks) {
+            const int n = c + 2;
+            GRMX_WAIT(&bar_full[n % kStages], n / kStages)
+            GRMX_WAIT(&bar_o_done[g], c / 2)       // O_c has consumed P_c: the S/P buffer is free
+            tc_fence_after();
+            issue_s(n);
           }
         }
       } while (false);
     }
-  } else if (warp < 4) {
-    // ===================================================================== P group
-    const int row = tid;                      // token row within the chunk == TMEM lane
-    const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-
-    auto vw_pass = [&](int c) {
-      const int len = chunk_len(c_begin + c);
-      const int step = rev ? kChunk - 1 - row : row;
-      const float w = step < len ? p.update_coeff * s_pow[len - 1 - step] : 0.0f;
-      const uint8_t* src = stage_v(c % kStages) + row * 128;
-      uint8_t* dst = vw_buf(c & 1) + row * 128;
+  } else if (warp >= kCopyWarp0) {
+    // ===================================================================== copy group (warps 8-9)
+    const int row0 = tid - kCopyWarp0 * 32;       // this thread copies token rows row0 and row0 + 64
+    for (int c = 0; c < n_chunks; ++c) {
+      GRMX_WAIT(&bar_full[c % kStages], c / kStages)
+      if (c >= 2) GRMX_WAIT(&bar_d_done[c & 1], c / 2 - 1)
+      const int g = c_begin + c;
+      const int len = chunk_len(g);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int ch = (i + row) & 7;   // rotate so that 8 neighbouring rows hit 8 bank groups
-        uint4 raw = *reinterpret_cast<const uint4*>(src + ch * 16);
-        uint32_t* words = reinterpret_cast<uint32_t*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float lo = __uint_as_float(words[j] << 16) * w;
-          const float hi = __uint_as_float(words[j] & 0xffff0000u) * w;
-          words[j] = pack_bf16(lo, hi);
-        }
-        *reinterpret_cast<uint4*>(dst + ch * 16) = raw;
+      for (int h = 0; h < 2; ++h) {
+        const int row = row0 + 64 * h;
+        const int step = rev ? kChunk - 1 - row : row;
+        const bool live = step < len;
+        const float w_v = live ? p.update_coeff * s_pow[len - 1 - step] : 0.0f;
+        const float w_q = live ? p.hidden_scale * s_pow[step + 1 - first_offset(g)] : 0.0f;
+        scaled_row_copy(stage_v(c % kStages), vw_buf(c & 1), row, w_v);
+        scaled_row_copy(stage_q(c % kStages), qs_buf(c & 1), row, w_q);
       }
       fence_proxy_async();
-      mbar_arrive(&bar_vw_ready[c & 1]);
-    };
-
-    do {
-      GRMX_WAIT(&bar_full[0], 0)
-      vw_pass(0);
-      for (int c = 0; c < n_chunks; ++c) {
-        GRMX_WAIT(&bar_s_done[c & 1], c / 2)
-        tc_fence_after();
-        // S_c -> P_c in place.  Warp w owns rows 32w..32w+31, so 32-column blocks above block w
-        // (below it in a reverse scan) are all zero.  P block b (16 packed columns) overwrites the S columns 16b..16b+15, which
-        // belong to S blocks 0 and 1: those two are in registers before anything is stored.
-        const uint32_t so_row = tmem_lane + kColSO + 128u * (c & 1);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t sv[2][32];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int blk = 2 * half + u;
-            if (rev ? blk >= warp : blk <= warp) tc_ld32_async(so_row + 32u * blk, sv[u]);
-          }
-          tc_wait_ld();
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int blk = 2 * half + u;
-            uint32_t pk[16];
-            if (rev ? blk >= warp : blk <= warp) {
-              const int m0 = 127 - row + 32 * blk;            // reversed-table index of column 32*blk
-              const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
-#pragma unroll
-              for (int t = 0; t < 8; ++t) {
-                const float4 w4 = wv[t];
-                pk[2 * t] = pack_bf16(__uint_as_float(sv[u][4 * t]) * w4.x, __uint_as_float(sv[u][4 * t + 1]) * w4.y);
-                pk[2 * t + 1] =
-                    pack_bf16(__uint_as_float(sv[u][4 * t + 2]) * w4.z, __uint_as_float(sv[u][4 * t + 3]) * w4.w);
-              }
-            } else {
-#pragma unroll
-              for (int t = 0; t < 16; ++t) pk[t] = 0u;
-            }
-            tc_st16_async(so_row + 16u * blk, pk);
-          }
-        }
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(&bar_p_ready[c & 1]);
-
-        if (c + 1 < n_chunks) {
-          const int n = c + 1;
-          GRMX_WAIT(&bar_full[n % kStages], n / kStages)
-          if (n >= 2) GRMX_WAIT(&bar_d_done[n & 1], n / 2 - 1)
-          vw_pass(n);
-        }
-      }
-    } while (false);
+      mbar_arrive(&bar_vq_ready[c & 1]);
+    }
   } else {
-    // ===================================================================== E group (warps 4-7)
-    const int quarter = warp - 4;
-    const int row = tid - 128;                // token row within the chunk == TMEM lane
+    // ===================================================================== compute groups (warps 0-7)
+    const int g = warp >> 2;                  // group 0: even chunks, group 1: odd chunks
+    const int quarter = warp & 3;
+    const int row = tid & 127;                // token row within the chunk == TMEM lane
+    const int step = rev ? kChunk - 1 - row : row;
     const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const uint32_t s_row = tmem_lane + kColS + 128u * g;
+    const uint32_t o_row = tmem_lane + kColO + 64u * g;
     const bool owns_row = lane < 16;          // M = 64 accumulator: lanes 0-15 of each quarter
     const int state_row = quarter * 16 + (lane & 15);
-    const int step = rev ? kChunk - 1 - row : row;   // processing step of this thread's token row
     // decay applied to the carried state over chunk c (the state in TMEM is kept pre-scaled by it)
     auto carry_of = [&](int c) { return s_pow[chunk_len(c_begin + c) - first_offset(c_begin + c)]; };
 
@@ -362,8 +344,8 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       }
     };
 
-    // initial state -> bf16 copy + TMEM (pre-scaled by the first chunk's carry)
-    {
+    if (g == 0) {
+      // state at the start of this CTA's chunks -> bf16 copy + TMEM (pre-scaled by the first carry)
       const float* m_in = static_cast<const float*>(p.memory_in) + b * kD * kD;
       const bool dense = p.m_col_stride == 1;
 #pragma unroll 1
@@ -388,20 +370,20 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             v[j] = owns_row ? m_in[state_row * p.m_row_stride + (c0 + j) * p.m_col_stride] : 0.0f;
           }
         }
-        // state at the start of this piece: M <- decay^(tokens of piece q - offset) M + partial_q
+        // pieces before this one: M <- decay^(tokens of piece q - offset) M + partial_q
         for (int q = 0; q < piece; ++q) {
           const int q_tokens = min(split.chunks_per_piece * kChunk, T - q * split.chunks_per_piece * kChunk);
-          const float g = powf(p.decay, static_cast<float>(q_tokens - first_offset(q * split.chunks_per_piece)));
+          const float gq = powf(p.decay, static_cast<float>(q_tokens - first_offset(q * split.chunks_per_piece)));
           if (owns_row) {
             const float4* part = reinterpret_cast<const float4*>(
                 split.partials + ((b * (split.pieces - 1) + q) * kD + state_row) * kD + c0);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const float4 x = __ldg(part + j);
-              v[4 * j] = fmaf(g, v[4 * j], x.x);
-              v[4 * j + 1] = fmaf(g, v[4 * j + 1], x.y);
-              v[4 * j + 2] = fmaf(g, v[4 * j + 2], x.z);
-              v[4 * j + 3] = fmaf(g, v[4 * j + 3], x.w);
+              v[4 * j] = fmaf(gq, v[4 * j], x.x);
+              v[4 * j + 1] = fmaf(gq, v[4 * j + 1], x.y);
+              v[4 * j + 2] = fmaf(gq, v[4 * j + 2], x.z);
+              v[4 * j + 3] = fmaf(gq, v[4 * j + 3], x.w);
             }
           }
         }
@@ -413,18 +395,59 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(bar_state_ready);   // phase 0
+      mbar_arrive(bar_state_ready);   // completion 0
     }
 
-    do {
-      for (int c = 0; c < n_chunks; ++c) {
-        const bool last = c + 1 == n_chunks;
-        // ---- state pass: M_c is complete ----
-        GRMX_WAIT(&bar_d_done[c & 1], c / 2)
-        tc_fence_after();
-        float* m_out = (p.memory_out != nullptr && piece + 1 == split.pieces)
+    for (int c = g; c < n_chunks; c += 2) {
+      const bool last = c + 1 == n_chunks;
+      // ---- P pass: S_c -> P_c in place ----
+      // Warp w owns rows 32w..32w+31, so 32-column blocks above block w (below it in a reverse
+      // scan) are all zero.  P block b (16 packed columns) overwrites the S columns 16b..16b+15,
+      // which belong to S blocks 0 and 1: those two are in registers before anything is stored.
+      GRMX_WAIT(&bar_s_done[g], c / 2)
+      tc_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sv[2][32];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int blk = 2 * half + u;
+          if (rev ? blk >= quarter : blk <= quarter) tc_ld32_async(s_row + 32u * blk, sv[u]);
+        }
+        tc_wait_ld();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int blk = 2 * half + u;
+          uint32_t pk[16];
+          if (rev ? blk >= quarter : blk <= quarter) {
+            const int m0 = 127 - row + 32 * blk;            // reversed-table index of column 32*blk
+            const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              const float4 w4 = wv[t];
+              pk[2 * t] = pack_bf16(__uint_as_float(sv[u][4 * t]) * w4.x, __uint_as_float(sv[u][4 * t + 1]) * w4.y);
+              pk[2 * t + 1] =
+                  pack_bf16(__uint_as_float(sv[u][4 * t + 2]) * w4.z, __uint_as_float(sv[u][4 * t + 3]) * w4.w);
+            }
+          } else {
+#pragma unroll
+            for (int t = 0; t < 16; ++t) pk[t] = 0u;
+          }
+          tc_st16_async(s_row + 16u * blk, pk);
+        }
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar_p_ready[g]);
+
+      // ---- state pass: M_c is complete ----
+      GRMX_WAIT(&bar_d_done[g], c / 2)
+      tc_fence_after();
+      {
+        float* m_out = (last && p.memory_out != nullptr && piece + 1 == split.pieces)
                            ? static_cast<float*>(p.memory_out) + b * kD * kD
                            : nullptr;
+        const float carry = last ? 0.0f : carry_of(c + 1);
 #pragma unroll 1
         for (int c0 = 0; c0 < kD; c0 += 32) {
           float v[32];
@@ -443,7 +466,6 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             }
           } else {
             if (owns_row) write_mb(v, c0);
-            const float carry = carry_of(c + 1);
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= carry;
             tc_st32(tmem_lane + kColM + c0, v);
@@ -452,45 +474,39 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         if (!last) {
           fence_proxy_async();
           tc_fence_before();
-          mbar_arrive(bar_state_ready);   // phase c + 1
+          mbar_arrive(bar_state_ready);   // completion c + 1
         }
-        // ---- epilogue: out row = O1 + hidden_scale * decay^(row+1) * O2 ----
-        GRMX_WAIT(&bar_o1_done[c & 1], c / 2)
-        tc_fence_after();
+      }
+
+      // ---- epilogue: O_c -> bf16 -> HBM ----
+      GRMX_WAIT(&bar_o_done[g], c / 2)
+      tc_fence_after();
+      {
         const bool row_live = step < chunk_len(c_begin + c);
-        const float row_scale = p.hidden_scale * s_pow[step + 1 - first_offset(c_begin + c)];
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.hidden_out) +
                              (b * p.T + static_cast<int64_t>(chunk_token0(c_begin + c)) + row) * kD;
-        {
-          uint32_t o1[2][32], o2[2][32];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            tc_ld32_async(tmem_lane + kColSO + 128u * (c & 1) + 64u + 32u * h, o1[h]);
-            tc_ld32_async(tmem_lane + kColO2 + 64u * (c & 1) + 32u * h, o2[h]);
-          }
-          tc_wait_ld();
+        uint32_t o[2][32];
+        tc_ld32_async(o_row, o[0]);
+        tc_ld32_async(o_row + 32u, o[1]);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&bar_o_free[g]);     // the values are in registers: the O buffer may be reused
+        if (row_live) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
-              float x[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                x[j] = fmaf(row_scale, __uint_as_float(o2[h][ch * 8 + j]), __uint_as_float(o1[h][ch * 8 + j]));
-              }
               uint4 w;
-              w.x = pack_bf16(x[0], x[1]);
-              w.y = pack_bf16(x[2], x[3]);
-              w.z = pack_bf16(x[4], x[5]);
-              w.w = pack_bf16(x[6], x[7]);
-              if (row_live) *reinterpret_cast<uint4*>(out + 32 * h + ch * 8) = w;
+              w.x = pack_bf16(__uint_as_float(o[h][ch * 8 + 0]), __uint_as_float(o[h][ch * 8 + 1]));
+              w.y = pack_bf16(__uint_as_float(o[h][ch * 8 + 2]), __uint_as_float(o[h][ch * 8 + 3]));
+              w.z = pack_bf16(__uint_as_float(o[h][ch * 8 + 4]), __uint_as_float(o[h][ch * 8 + 5]));
+              w.w = pack_bf16(__uint_as_float(o[h][ch * 8 + 6]), __uint_as_float(o[h][ch * 8 + 7]));
+              *reinterpret_cast<uint4*>(out + 32 * h + ch * 8) = w;
             }
           }
         }
-        tc_fence_before();
-        mbar_arrive(&bar_acc_free[c & 1]);
       }
-    } while (false);
+    }
   }
 #undef GRMX_WAIT
 
