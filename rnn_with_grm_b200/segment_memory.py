@@ -1,0 +1,231 @@
+"""The callers on either side of the kernels: archive, segment loop, stacked model.
+
+``SegmentMemoryRunner.forward`` is the segment loop of the reference's
+``SegmentRecurrentMemoryModel.forward`` (grm/core/paper_grm.py:647-747) driven by this
+engine's kernels, with two structural changes that leave results unchanged:
+
+* the archive is a preallocated device ring ``[B, capacity, H, K]`` written in place at the end
+  of each segment, instead of a deque of tensors that is re-stacked and permuted for every
+  segment (paper_grm.py:135-146, 227-228);
+* gather, apply-query, gate-weighted sum, residual and LayerNorm are one kernel
+  (``torch.ops.grmx.retrieve_fuse``) that reads the selected matrices straight from the ring, so
+  the ``[B, C, R, H, K]`` tensor of paper_grm.py:229-234 never exists.
+
+Parameters are taken by the names of the reference model's ``state_dict`` so a checkpoint of
+the reference loads as is.  Projections and the weight-bearing fusion rules are plain
+``torch.nn.functional`` calls (cuBLAS); everything on the memory path goes through
+``cuda_ops`` / ``torch.ops.grmx``.  CUDA only, inference only (no autograd through the ring).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from . import cuda_ops
+
+FUSE_RETRIEVED, FUSE_CONTRIB, FUSE_RESIDUAL_LN = 0, 1, 2
+
+
+class SegmentMemoryArchive:
+    """Bounded FIFO of segment-end memories and segment summaries, resident on the device.
+
+    Same contract as the reference's ``_BatchMemoryArchive`` (paper_grm.py:31-44): at most
+    ``capacity`` segments, the oldest evicted first, and routing indices are positions in
+    the current FIFO order (0 = oldest).
+    """
+
+    def __init__(self, batch: int, capacity: int, hidden: int, key_dim: int, summary_dim: int, device):
+        self.capacity = int(capacity)
+        self.memories = torch.empty(batch, self.capacity, hidden, key_dim, device=device, dtype=torch.float32)
+        self.summaries = torch.empty(batch, self.capacity, summary_dim, device=device, dtype=torch.float32)
+        self.count = 0      # segments held
+        self.head = 0       # physical slot of the oldest segment
+        self.total_pushed = 0
+
+    def push(self, memory: Tensor, summary: Tensor) -> None:
+        slot = (self.head + self.count) % self.capacity
+        self.memories[:, slot].copy_(memory)
+        self.summaries[:, slot].copy_(summary)
+        if self.count < self.capacity:
+            self.count += 1
+        else:
+            self.head = (self.head + 1) % self.capacity
+        self.total_pushed += 1
+
+    def ordered_summaries(self) -> Tensor:
+        """``[B, count, D]`` in FIFO order."""
+        if self.head == 0:
+            return self.summaries[:, : self.count]
+        order = (torch.arange(self.count, device=self.summaries.device) + self.head) % self.capacity
+        return self.summaries.index_select(1, order)
+
+    def physical_indices(self, indices: Tensor) -> Tensor:
+        """FIFO positions -> slots of ``self.memories`` (empty slots, -1, stay -1)."""
+        if self.head == 0:
+            return indices
+        return torch.where(indices >= 0, (indices + self.head) % self.capacity, indices)
+
+
+def _linear(x: Tensor, params: Dict[str, Tensor], name: str) -> Tensor:
+    return F.linear(x, params[f"{name}.weight"], params.get(f"{name}.bias"))
+
+
+class SegmentMemoryRunner:
+    """One segment-memory layer: scan -> route -> retrieve + fuse -> output projection."""
+
+    def __init__(self, params: Dict[str, Tensor], *, segment_length: int, retrieval_top_k: int,
+                 memory_capacity_segments: int, memory_decay: float = 0.97,
+                 retrieval_fusion_mode: str = "residual", memory_initialization_mode: str = "checkpoint",
+                 use_layer_norm: bool = True, layer_norm_eps: float = 1e-5, temperature: float = 1.0):
+        if retrieval_fusion_mode not in ("residual", "concat", "gate", "linear"):
+            raise ValueError(f"Unknown retrieval_fusion_mode: {retrieval_fusion_mode}")
+        self.p = params
+        self.segment_length = int(segment_length)
+        self.top_k = int(retrieval_top_k)
+        self.capacity = int(memory_capacity_segments)
+        self.decay = float(memory_decay)
+        self.mode = retrieval_fusion_mode
+        self.init_mode = memory_initialization_mode
+        self.use_layer_norm = use_layer_norm
+        self.eps = float(layer_norm_eps)
+        self.temperature = float(temperature)
+        self.hidden = params["memory_cell.value_proj.weight"].shape[0]
+        self.key_dim = params["memory_cell.key_proj.weight"].shape[0]
+        self.input_size = params["memory_cell.key_proj.weight"].shape[1]
+        self.route_dim = params["gating_unit.query_projection.weight"].shape[0]
+        self.archive: Optional[SegmentMemoryArchive] = None
+
+    def clear_memory(self) -> None:
+        self.archive = None
+
+    # ---- pieces of one segment -------------------------------------------------------------
+
+    def _scan(self, x: Tensor, memory: Tensor) -> Tuple[Tensor, Tensor]:
+        # paper_grm.py:491-504
+        k = F.normalize(_linear(x, self.p, "memory_cell.key_proj"), p=2, dim=-1, eps=1e-6)
+        v = _linear(x, self.p, "memory_cell.value_proj")
+        q = F.normalize(_linear(x, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6)
+        return cuda_ops.cuda_chunk_update(k, v, q, memory, self.decay)
+
+    def _route(self, x: Tensor, summaries: Tensor) -> Tuple[Tensor, Tensor]:
+        # paper_grm.py:566-589: bias-free projections, scale 1/sqrt(route_dim), top-k, softmax
+        q_proj = F.linear(x.float(), self.p["gating_unit.query_projection.weight"].float())
+        k_proj = F.linear(summaries, self.p["gating_unit.key_projection.weight"].float())
+        gates, indices, _ = torch.ops.grmx.topk_route(q_proj, k_proj, None, self.top_k,
+                                                      1.0 / math.sqrt(self.route_dim), self.temperature, False)
+        return gates, indices
+
+    def _retrieve_and_fuse(self, x: Tensor, h_online: Tensor, gates: Tensor, indices: Tensor) -> Tensor:
+        archive = self.archive
+        q_t = F.normalize(_linear(x, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6).float()
+        phys = archive.physical_indices(indices)
+        ln_w = self.p.get("aggregator.layer_norm.weight") if self.use_layer_norm else None
+        ln_b = self.p.get("aggregator.layer_norm.bias") if self.use_layer_norm else None
+        if self.mode == "residual" and self.use_layer_norm and "aggregator.output_projection.weight" not in self.p:
+            fused = torch.ops.grmx.retrieve_fuse(archive.memories, phys, gates, q_t, h_online.float(), ln_w, ln_b,
+                                                 self.eps, FUSE_RESIDUAL_LN)
+            return fused.to(h_online.dtype)
+        contrib = torch.ops.grmx.retrieve_fuse(archive.memories, phys, gates, q_t, None, None, None, self.eps,
+                                               FUSE_CONTRIB).to(h_online.dtype)
+        # aggregator.py:116-145
+        if self.mode == "residual":
+            fused = h_online + contrib
+            if "aggregator.output_projection.weight" in self.p:
+                fused = _linear(fused, self.p, "aggregator.output_projection")
+        elif self.mode == "concat":
+            fused = _linear(torch.cat([h_online, contrib], dim=-1), self.p, "aggregator.output_projection")
+        elif self.mode == "gate":
+            gate = torch.sigmoid(_linear(torch.cat([h_online, contrib], dim=-1), self.p, "aggregator.gate_projection"))
+            fused = gate * h_online + (1.0 - gate) * contrib
+        else:
+            fused = _linear(h_online, self.p, "aggregator.online_projection") + \
+                _linear(contrib, self.p, "aggregator.memory_projection")
+        if self.use_layer_norm:
+            fused = F.layer_norm(fused, (self.hidden,), ln_w, ln_b, self.eps)
+        return fused
+
+    # ---- the segment loop ------------------------------------------------------------------
+
+    @torch.no_grad()
+    def forward(self, x_seq: Tensor, c_init: Optional[Tensor] = None, reset_memory: bool = False,
+                return_routes: bool = False):
+        """``x_seq [B, T, D]`` -> ``(outputs [B, T, out], h_final [B, H], memory_final [B, H, K], aux)``."""
+        if x_seq.device.type != "cuda":
+            raise RuntimeError("SegmentMemoryRunner needs CUDA tensors; this engine has no CPU path")
+        B, T, _ = x_seq.shape
+        if reset_memory:
+            self.clear_memory()
+        if self.archive is None:
+            self.archive = SegmentMemoryArchive(B, self.capacity, self.hidden, self.key_dim, self.input_size,
+                                                x_seq.device)
+        archive = self.archive
+        # the carried state stays fp32 whatever the activations are
+        memory = c_init.float() if c_init is not None else torch.zeros(B, self.hidden, self.key_dim,
+                                                                       device=x_seq.device, dtype=torch.float32)
+        if x_seq.dtype == torch.float32:
+            memory = memory.float()
+        outputs: List[Tensor] = []
+        routes = []
+        last_hidden = torch.zeros(B, self.hidden, device=x_seq.device, dtype=x_seq.dtype)
+        for start in range(0, T, self.segment_length):
+            x = x_seq[:, start:start + self.segment_length]
+            h_online, memory = self._scan(x, memory)
+            if archive.count > 0:                                   # paper_grm.py:620-621: no fusion otherwise
+                gates, indices = self._route(x, archive.ordered_summaries())
+                h = self._retrieve_and_fuse(x, h_online, gates, indices)
+                if return_routes:
+                    routes.append((gates, indices))
+            else:
+                h = h_online
+            outputs.append(_linear(h, self.p, "output_proj"))
+            last_hidden = h[:, -1]
+            archive.push(memory, x.float().mean(dim=1))            # paper_grm.py:522-523, 721-725
+            if self.init_mode == "independent":
+                memory = torch.zeros_like(memory)
+        out = torch.cat(outputs, dim=1) if outputs else x_seq.new_zeros(B, 0, self.p["output_proj.weight"].shape[0])
+        aux = {"num_segments": archive.count, "total_pushed": archive.total_pushed}
+        if return_routes:
+            aux["routes"] = routes
+        return out, last_hidden, memory, aux
+
+
+class StackedSegmentMemoryRunner:
+    """``HierarchicalSegmentMemoryModel`` (grm/core/multilayer_grm.py:105-220), optionally under the
+    language-model wrapper (embedding + vocabulary projection, grm/utils/train.py:192-225).
+
+    ``params`` uses the reference names: ``layers.<i>.grm.<...>``, ``layers.<i>.layer_norm.*``,
+    ``output_proj.*`` and, for the language model, ``embedding.weight`` / ``output_layer.*`` with the
+    stack under ``grm_rnn.``.
+    """
+
+    def __init__(self, params: Dict[str, Tensor], num_layers: int, *, language_model: bool = False, **layer_kwargs):
+        prefix = "grm_rnn." if language_model else ""
+        self.language_model = language_model
+        self.params = params
+        self.prefix = prefix
+        self.layers = []
+        for i in range(num_layers):
+            base = f"{prefix}layers.{i}.grm."
+            sub = {k[len(base):]: v for k, v in params.items() if k.startswith(base)}
+            self.layers.append(SegmentMemoryRunner(sub, **layer_kwargs))
+        self.num_layers = num_layers
+
+    @torch.no_grad()
+    def forward(self, x: Tensor, reset_memory: bool = True):
+        p, pre = self.params, self.prefix
+        h = F.embedding(x, p["embedding.weight"]) if self.language_model else x
+        finals = []
+        for i, layer in enumerate(self.layers):
+            out, _, memory, _ = layer.forward(h, reset_memory=reset_memory)
+            w, b = p.get(f"{pre}layers.{i}.layer_norm.weight"), p.get(f"{pre}layers.{i}.layer_norm.bias")
+            h = F.layer_norm(out + h, (h.shape[-1],), w, b, 1e-5)       # multilayer_grm.py:88-92
+            finals.append(memory)
+        y = F.linear(h, p[f"{pre}output_proj.weight"], p.get(f"{pre}output_proj.bias"))
+        if self.language_model:
+            y = F.linear(y, p["output_layer.weight"], p.get("output_layer.bias"))
+        return y, torch.stack(finals, dim=0)

@@ -16,6 +16,9 @@ reference's Python implementation on CPU in float32:
                              examples/test_grm.py:203-210.
 * ``retriever_*.npz``     -- ``TopKMemoryRetriever.forward`` (weights included).
 * ``fusion_*.npz``        -- ``RetrievedStateFusion.forward`` for the four weight-bearing modes.
+* ``model_cfg4.npz``      -- samples of the 4-layer ``SegmentMemoryLanguageModel`` forward at config 4
+                             (B=8, T=8192, hidden 512, vocab 32768; ``--only model_cfg4``, ~2 min),
+                             weights rebuilt from ``seeded_weights.py``.
 * ``model_cfg1.npz``      -- ``SegmentRecurrentMemoryModel`` forward on the single-layer
                              adding-problem configuration (weights, inputs, outputs, final
                              state and every segment's routing indices and gates).
@@ -193,13 +196,55 @@ def model_cfg1_case():
     )
 
 
+def model_cfg4_case():
+    """4-layer language model of config 4 at full size; only samples of the outputs are stored
+    (the weights are rebuilt from seeded_weights.py on both sides)."""
+    import time
+
+    from grm.core.multilayer_grm import HierarchicalSegmentMemoryModel
+    from grm.utils.train import SegmentMemoryLanguageModel
+
+    sys.path.insert(0, str(HERE))
+    from seeded_weights import seeded_state_dict, zipf_token_ids
+
+    vocab, hidden, layers, seq, batch = 32768, 512, 4, 8192, 8
+    stack = HierarchicalSegmentMemoryModel(
+        hidden, hidden, hidden, num_layers=layers, segment_length=512, memory_key_dim=64, retrieval_top_k=4,
+        memory_capacity_segments=16, memory_storage_dtype=torch.float32, recomputation_ratio=0.0, dropout=0.0,
+        cuda_cpp_debug_fallback=True)
+    model = SegmentMemoryLanguageModel(stack, vocab_size=vocab, embed_dim=hidden).eval()
+    shapes = {k: tuple(v.shape) for k, v in model.state_dict().items()
+              if isinstance(v, torch.Tensor) and "memory_bank" not in k}
+    missing = model.load_state_dict(seeded_state_dict(shapes), strict=False)
+    assert not missing.unexpected_keys
+    ids = zipf_token_ids(batch, seq, vocab, 1.1, seed=0)
+    torch.set_num_threads(8)
+    t0 = time.time()
+    with torch.no_grad():
+        logits, h_final, c_final, aux = model(ids, reset_memory=True)
+    print(f"config-4 reference forward: {time.time() - t0:.1f} s")
+    positions = torch.tensor([0, 1, 511, 512, 513, 1023, 1024, 2047, 4095, 4096, 6000, 8190, 8191])
+    np.savez_compressed(
+        HERE / "model_cfg4.npz",
+        positions=positions.numpy(), logits=logits[:, positions, :256].numpy(),
+        logit_row_norms=logits[:, positions].norm(dim=-1).numpy(),
+        c_final=c_final[:, :, :16, :16].numpy(), c_final_norm=c_final.flatten(2).norm(dim=-1).numpy(),
+        num_segments=np.int64(aux["num_segments"]),
+        shape_names=np.array(list(shapes.keys())), shape_dims=np.array([str(v) for v in shapes.values()]),
+    )
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--reference", type=Path, default=Path("/root/reference"))
+    parser.add_argument("--only", default="", help="generate only this fixture (e.g. model_cfg4)")
     args = parser.parse_args(argv)
     sys.dont_write_bytecode = True
     sys.path.insert(0, str(args.reference))
     torch.set_num_threads(1)
+    if args.only == "model_cfg4":
+        model_cfg4_case()
+        return 0
     chunk_case("small", 1, B=2, T=8, K=8, H=16, decay=0.97)        # shape of examples/test_grm.py:29-37
     chunk_case("ragged", 2, B=3, T=67, K=6, H=5, decay=0.9)
     chunk_case("cfg1", 3, B=2, T=128, K=64, H=128, decay=0.97, zero_state=True)
