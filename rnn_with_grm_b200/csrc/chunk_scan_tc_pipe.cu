@@ -12,9 +12,10 @@
 // which is the closed form of the reference chunk (grm/core/cuda_ops.py:218-254) with the state
 // carried across chunks as in grm/csrc/grm_cuda.cpp:67-83.  Roles:
 //
-//   warp 11      TMA producer: q/k/v tiles into a 3-stage ring
-//   warp 10      MMA issuer (one thread): O_c(state part), M_c | O_c(P part) | S_{c+2}
-//   warps 8-9    copy group: Vw_c and Qs_c, the two decay-scaled copies, ahead of the issuer
+//   warp 12      issuer A (one thread): O_c(P part) | S_{c+2} | TMA loads of chunk c+3 (3-stage ring)
+//   warp 13      issuer B (one thread): O_c(state part), M_c  -- the only products on the
+//                recurrence, so that the serial chain is state pass -> 12 MMAs -> state pass
+//   warps 8-11   copy group: Vw_c and Qs_c, the two decay-scaled copies, ahead of the issuer
 //   warps 0-3    compute group 0, chunks 0, 2, 4, ...
 //   warps 4-7    compute group 1, chunks 1, 3, 5, ...
 //                each: S_c -> P_c (decay mask, bf16, written back into the TMEM columns of S_c),
@@ -41,11 +42,11 @@ using namespace tc;
 constexpr int kChunk = 128;
 constexpr int kD = 64;                 // d_k == d_v
 constexpr int kStages = 3;
-constexpr int kThreads = 384;          // 12 warps: 168 registers per thread, no spills
-constexpr int kCopyWarp0 = 8;          // warps 8-9, two token rows per thread
-constexpr int kCopyThreads = 64;
-constexpr int kMmaWarp = 10;
-constexpr int kTmaWarp = 11;
+constexpr int kThreads = 448;          // 14 warps (registers are granted as for 16: 128 per thread)
+constexpr int kCopyWarp0 = 8;          // warps 8-11, one token row per thread
+constexpr int kCopyThreads = 128;
+constexpr int kIssuerA = 12;           // S, P part of O, TMA; also owns the TMEM allocation
+constexpr int kIssuerB = 13;           // state part of O, state update
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;          // + 128 * group : S (128 cols), then P in cols 0-63 (bf16 pairs)
 constexpr uint32_t kColO = 256;        // + 64 * group  : O
@@ -88,15 +89,19 @@ __device__ __forceinline__ void scaled_row_copy(const uint8_t* src_tile, uint8_t
   const uint8_t* src = src_tile + row * 128;
   uint8_t* dst = dst_tile + row * 128;
   const __nv_bfloat162 w2 = __float2bfloat162_rn(w);
+  // all eight loads first: source and destination could alias as far as the compiler knows, and
+  // a load-store-load-store sequence would serialise on the shared-memory latency
+  uint4 raw[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(src + ((i + row) & 7) * 16);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int ch = (i + row) & 7;
-    uint4 raw = *reinterpret_cast<const uint4*>(src + ch * 16);
-    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw[i]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) pairs[j] = __hmul2(pairs[j], w2);
-    *reinterpret_cast<uint4*>(dst + ch * 16) = raw;
   }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(dst + ((i + row) & 7) * 16) = raw[i];
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -109,10 +114,9 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   float* s_pow = reinterpret_cast<float*>(smem + kOffPow);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   uint64_t* bar_full = bars;              // [3] TMA bytes landed                             (1 + tx)
-  uint64_t* bar_stage_free = bars + 3;    // [3] last MMA reading the stage retired           (commit)
   uint64_t* bar_s_done = bars + 6;        // [2] S_c complete                                 (commit)
   uint64_t* bar_p_ready = bars + 8;       // [2] P_c in TMEM                                  (128)
-  uint64_t* bar_vq_ready = bars + 10;     // [2] Vw_c and Qs_c written                        (64)
+  uint64_t* bar_vq_ready = bars + 10;     // [2] Vw_c and Qs_c written                        (128)
   uint64_t* bar_d_done = bars + 12;       // [2] state part of O_c and M_c complete           (commit)
   uint64_t* bar_o_done = bars + 14;       // [2] O_c complete                                 (commit)
   uint64_t* bar_o_free = bars + 16;       // [2] epilogue c has read O_c                      (128)
@@ -145,7 +149,6 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) {
       mbar_init(&bar_full[i], 1);
-      mbar_init(&bar_stage_free[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_s_done[i], 1);
@@ -166,7 +169,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     const int d = rev ? m - 127 : 127 - m;
     s_wtab[j] = d >= 0 ? p.hidden_scale * p.update_coeff * powf(p.decay, static_cast<float>(d)) : 0.0f;
   }
-  if (warp == kMmaWarp) {
+  if (warp == kIssuerA) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
                  "r"(kTmemCols)
                  : "memory");
@@ -193,43 +196,30 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   // barrier X that belongs to chunk c (phase c/2 of X[c&1], phase c/3 of X[c%3]).  A waiter is
   // never more than one completion behind, because the producer's next completion on the same
   // barrier needs something that comes after the waiter's wait:
-  //   issuer:  O_c(state part), M_c  need vq_ready(c)    <- copy group     <- full(c), d_done(c-2)
+  //   issuer B: O_c(state part), M_c need vq_ready(c)    <- copy group     <- full(c), d_done(c-2)
   //                                       state_ready(c) <- state pass c-1 <- d_done(c-1)
   //                                       o_free(c-2)    <- epilogue c-2   <- o_done(c-2)
-  //            O_c(P part)           needs p_ready(c)    <- P pass c       <- s_done(c)
-  //            S_{c+2}               needs o_done(c) (O_c reads its S/P buffer) and full(c+2)
-  //   TMA:     chunk c               needs stage_free(c-3) <- O_{c-3}
+  //   issuer A: O_c(P part)          needs p_ready(c)    <- P pass c       <- s_done(c)
+  //                                        d_done(c)     (the state part is accumulated first)
+  //             S_{c+2}              needs o_done(c) (O_c reads its S/P buffer) and full(c+2)
+  //             TMA of chunk c+3     needs o_done(c): every reader of stage c%3 has retired
 
-  if (warp == kTmaWarp) {
-    // ===================================================================== TMA producer
+  if (warp == kIssuerA) {
+    // ===================================================================== issuer A + TMA
     if (lane == 0) {
-      int issued = 0;
-      for (int c = 0; c < n_chunks; ++c) {
+      constexpr uint32_t idesc_s = make_idesc(kChunk, kChunk, 0, 0);
+      constexpr uint32_t idesc_op = make_idesc(kChunk, kD, 0, 1);
+      int loads_issued = 0;
+
+      auto issue_loads = [&](int c) {
         const int s = c % kStages;
-        if (c >= kStages) GRMX_WAIT(&bar_stage_free[s], c / kStages - 1)
         mbar_expect_tx(&bar_full[s], kStageBytes);
         const int t0 = chunk_token0(c_begin + c);
         tma_load_3d(stage_q(s), &map_q, &bar_full[s], 0, t0, static_cast<int>(b));
         tma_load_3d(stage_k(s), &map_k, &bar_full[s], 0, t0, static_cast<int>(b));
         tma_load_3d(stage_v(s), &map_v, &bar_full[s], 0, t0, static_cast<int>(b));
-        issued = c + 1;
-      }
-      if (*s_abort) {
-        // let the copies still in flight land before the shared memory is released
-        for (int c = issued > kStages ? issued - kStages : 0; c < issued; ++c) {
-          mbar_wait_quiet(&bar_full[c % kStages], (c / kStages) & 1);
-        }
-      }
-    }
-  } else if (warp == kMmaWarp) {
-    // ===================================================================== MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc(kChunk, kChunk, 0, 0);
-      constexpr uint32_t idesc_oq = make_idesc(kChunk, kD, 0, 0);
-      constexpr uint32_t idesc_m = make_idesc(kD, kD, 1, 1);
-      constexpr uint32_t idesc_op = make_idesc(kChunk, kD, 0, 1);
-      const uint64_t desc_mb = smem_desc(smem_u32(s_mb), 16, 1024);
-
+        loads_issued = c + 1;
+      };
       auto issue_s = [&](int c) {
         const int s = c % kStages;
         const uint64_t dq = smem_desc(smem_u32(stage_q(s)), 16, 1024);
@@ -242,6 +232,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         tc_commit(&bar_s_done[c & 1]);
       };
 
+      for (int c = 0; c < n_chunks && c < kStages; ++c) issue_loads(c);
       do {
         GRMX_WAIT(&bar_full[0], 0)
         tc_fence_after();
@@ -254,65 +245,77 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         for (int c = 0; c < n_chunks; ++c) {
           const int s = c % kStages;
           const int g = c & 1;
-          GRMX_WAIT(&bar_vq_ready[g], c / 2)
-          GRMX_WAIT(bar_state_ready, c)
-          if (c >= 2) GRMX_WAIT(&bar_o_free[g], c / 2 - 1)
-          tc_fence_after();
-          const uint32_t o_tmem = tmem_base + kColO + 64u * g;
-          {
-            const uint64_t dqs = smem_desc(smem_u32(qs_buf(g)), 16, 1024);
-            const uint64_t dk_mn = smem_desc(smem_u32(stage_k(s)), kTileBytes, 1024);
-            const uint64_t dvw = smem_desc(smem_u32(vw_buf(g)), kTileBytes, 1024);
-#pragma unroll
-            for (int kk = 0; kk < kD / 16; ++kk) {
-              tc_mma_bf16(o_tmem, desc_add(dqs, kk * 32), desc_add(desc_mb, kk * 32), idesc_oq, kk > 0);
-            }
-#pragma unroll
-            for (int kk = 0; kk < kChunk / 16; ++kk) {
-              tc_mma_bf16(tmem_base + kColM, desc_add(dvw, kk * 2048), desc_add(dk_mn, kk * 2048), idesc_m, 1u);
-            }
-            tc_commit(&bar_d_done[g]);
-          }
           GRMX_WAIT(&bar_p_ready[g], c / 2)
+          GRMX_WAIT(&bar_d_done[g], c / 2)
           tc_fence_after();
           {
             const uint64_t dv_mn = smem_desc(smem_u32(stage_v(s)), kTileBytes, 1024);
             const uint32_t p_tmem = tmem_base + kColS + 128u * g;   // 16 tokens of P = 8 columns
+            const uint32_t o_tmem = tmem_base + kColO + 64u * g;
 #pragma unroll
             for (int kk = 0; kk < kChunk / 16; ++kk) {
               tc_mma_bf16_ts(o_tmem, p_tmem + 8u * kk, desc_add(dv_mn, kk * 2048), idesc_op, 1u);
             }
             tc_commit(&bar_o_done[g]);
-            tc_commit(&bar_stage_free[s]);
           }
           if (c + 2 < n_chunks) {
-            const int n = c + 2;
-            GRMX_WAIT(&bar_full[n % kStages], n / kStages)
+            GRMX_WAIT(&bar_full[(c + 2) % kStages], (c + 2) / kStages)
             GRMX_WAIT(&bar_o_done[g], c / 2)       // O_c has consumed P_c: the S/P buffer is free
             tc_fence_after();
-            issue_s(n);
+            issue_s(c + 2);
+            if (c + 3 < n_chunks) issue_loads(c + 3);   // stage c % 3: all its readers retired with O_c
           }
         }
       } while (false);
+      if (*s_abort) {
+        // let the copies still in flight land before the shared memory is released
+        for (int c = loads_issued > kStages ? loads_issued - kStages : 0; c < loads_issued; ++c) {
+          mbar_wait_quiet(&bar_full[c % kStages], (c / kStages) & 1);
+        }
+      }
+    }
+  } else if (warp == kIssuerB) {
+    // ===================================================================== issuer B
+    if (lane == 0) {
+      constexpr uint32_t idesc_oq = make_idesc(kChunk, kD, 0, 0);
+      constexpr uint32_t idesc_m = make_idesc(kD, kD, 1, 1);
+      const uint64_t desc_mb = smem_desc(smem_u32(s_mb), 16, 1024);
+      for (int c = 0; c < n_chunks; ++c) {
+        const int s = c % kStages;
+        const int g = c & 1;
+        GRMX_WAIT(&bar_vq_ready[g], c / 2)
+        if (c >= 2) GRMX_WAIT(&bar_o_free[g], c / 2 - 1)
+        GRMX_WAIT(bar_state_ready, c)
+        tc_fence_after();
+        const uint64_t dqs = smem_desc(smem_u32(qs_buf(g)), 16, 1024);
+        const uint64_t dk_mn = smem_desc(smem_u32(stage_k(s)), kTileBytes, 1024);
+        const uint64_t dvw = smem_desc(smem_u32(vw_buf(g)), kTileBytes, 1024);
+        const uint32_t o_tmem = tmem_base + kColO + 64u * g;
+#pragma unroll
+        for (int kk = 0; kk < kChunk / 16; ++kk) {
+          tc_mma_bf16(tmem_base + kColM, desc_add(dvw, kk * 2048), desc_add(dk_mn, kk * 2048), idesc_m, 1u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          tc_mma_bf16(o_tmem, desc_add(dqs, kk * 32), desc_add(desc_mb, kk * 32), idesc_oq, kk > 0);
+        }
+        tc_commit(&bar_d_done[g]);
+      }
     }
   } else if (warp >= kCopyWarp0) {
-    // ===================================================================== copy group (warps 8-9)
-    const int row0 = tid - kCopyWarp0 * 32;       // this thread copies token rows row0 and row0 + 64
+    // ===================================================================== copy group (warps 8-11)
+    const int row = tid - kCopyWarp0 * 32;
+    const int step = rev ? kChunk - 1 - row : row;
     for (int c = 0; c < n_chunks; ++c) {
       GRMX_WAIT(&bar_full[c % kStages], c / kStages)
       if (c >= 2) GRMX_WAIT(&bar_d_done[c & 1], c / 2 - 1)
       const int g = c_begin + c;
       const int len = chunk_len(g);
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int row = row0 + 64 * h;
-        const int step = rev ? kChunk - 1 - row : row;
-        const bool live = step < len;
-        const float w_v = live ? p.update_coeff * s_pow[len - 1 - step] : 0.0f;
-        const float w_q = live ? p.hidden_scale * s_pow[step + 1 - first_offset(g)] : 0.0f;
-        scaled_row_copy(stage_v(c % kStages), vw_buf(c & 1), row, w_v);
-        scaled_row_copy(stage_q(c % kStages), qs_buf(c & 1), row, w_q);
-      }
+      const bool live = step < len;
+      const float w_v = live ? p.update_coeff * s_pow[len - 1 - step] : 0.0f;
+      const float w_q = live ? p.hidden_scale * s_pow[step + 1 - first_offset(g)] : 0.0f;
+      scaled_row_copy(stage_v(c % kStages), vw_buf(c & 1), row, w_v);
+      scaled_row_copy(stage_q(c % kStages), qs_buf(c & 1), row, w_q);
       fence_proxy_async();
       mbar_arrive(&bar_vq_ready[c & 1]);
     }
@@ -407,34 +410,27 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       GRMX_WAIT(&bar_s_done[g], c / 2)
       tc_fence_after();
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sv[2][32];
+      for (int blk = 0; blk < 4; ++blk) {
+        // P block blk lands on S columns 16*blk..16*blk+15, i.e. inside S block blk/2, which has been
+        // read by the time it is overwritten (blocks are visited in increasing order)
+        uint32_t pk[16];
+        if (rev ? blk >= quarter : blk <= quarter) {
+          uint32_t sv[32];
+          tc_ld32_async(s_row + 32u * blk, sv);
+          const int m0 = 127 - row + 32 * blk;            // reversed-table index of column 32*blk
+          const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
+          tc_wait_ld();
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int blk = 2 * half + u;
-          if (rev ? blk >= quarter : blk <= quarter) tc_ld32_async(s_row + 32u * blk, sv[u]);
-        }
-        tc_wait_ld();
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int blk = 2 * half + u;
-          uint32_t pk[16];
-          if (rev ? blk >= quarter : blk <= quarter) {
-            const int m0 = 127 - row + 32 * blk;            // reversed-table index of column 32*blk
-            const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-              const float4 w4 = wv[t];
-              pk[2 * t] = pack_bf16(__uint_as_float(sv[u][4 * t]) * w4.x, __uint_as_float(sv[u][4 * t + 1]) * w4.y);
-              pk[2 * t + 1] =
-                  pack_bf16(__uint_as_float(sv[u][4 * t + 2]) * w4.z, __uint_as_float(sv[u][4 * t + 3]) * w4.w);
-            }
-          } else {
-#pragma unroll
-            for (int t = 0; t < 16; ++t) pk[t] = 0u;
+          for (int t = 0; t < 8; ++t) {
+            const float4 w4 = wv[t];
+            pk[2 * t] = pack_bf16(__uint_as_float(sv[4 * t]) * w4.x, __uint_as_float(sv[4 * t + 1]) * w4.y);
+            pk[2 * t + 1] = pack_bf16(__uint_as_float(sv[4 * t + 2]) * w4.z, __uint_as_float(sv[4 * t + 3]) * w4.w);
           }
-          tc_st16_async(s_row + 16u * blk, pk);
+        } else {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) pk[t] = 0u;
         }
+        tc_st16_async(s_row + 16u * blk, pk);
       }
       tc_wait_st();
       tc_fence_before();
@@ -514,7 +510,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   tc_fence_before();
   __syncthreads();
   if (tid == 0 && *s_abort && error_word != nullptr) atomicOr(error_word, kErrBoundedWait);
-  if (warp == kMmaWarp) {
+  if (warp == kIssuerA) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                  : "memory");
   }
