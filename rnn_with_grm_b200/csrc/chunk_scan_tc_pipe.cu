@@ -79,31 +79,6 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // descriptor + byte offset (the start-address field holds addr >> 4 in its low 14 bits)
 __device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
 
-// One token row (128 bytes, 64 bf16) of a swizzled tile times a scalar, into another tile at the
-// same position.  The product is formed by the packed bf16 multiplier (exact product, one
-// rounding), with the scalar itself rounded to bf16 first: the copy is one instruction per two
-// elements, which matters because these copies are the largest block of plain instructions in
-// the kernel.  The 16-byte pieces of a row are visited in an order rotated by the row index so
-// that eight neighbouring rows touch eight different bank groups.
-__device__ __forceinline__ void scaled_row_copy(const uint8_t* src_tile, uint8_t* dst_tile, int row, float w) {
-  const uint8_t* src = src_tile + row * 128;
-  uint8_t* dst = dst_tile + row * 128;
-  const __nv_bfloat162 w2 = __float2bfloat162_rn(w);
-  // all eight loads first: source and destination could alias as far as the compiler knows, and
-  // a load-store-load-store sequence would serialise on the shared-memory latency
-  uint4 raw[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(src + ((i + row) & 7) * 16);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw[i]);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) pairs[j] = __hmul2(pairs[j], w2);
-  }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(dst + ((i + row) & 7) * 16) = raw[i];
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, ScanParams p, SplitInfo split,

@@ -156,21 +156,7 @@ piece_state_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       // weight of this token: every later token of the piece decays it once more
       const int later = piece_tokens - 1 - (c * kChunk + step);
       const float w = step < chunk_len(c_begin + c) ? p.update_coeff * powf(p.decay, static_cast<float>(later)) : 0.0f;
-      const uint8_t* src = stage_v(c % kStages) + row * 128;
-      uint8_t* dst = vw_buf(c & 1) + row * 128;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int ch = (i + row) & 7;
-        uint4 raw = *reinterpret_cast<const uint4*>(src + ch * 16);
-        uint32_t* words = reinterpret_cast<uint32_t*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float lo = __uint_as_float(words[j] << 16) * w;
-          const float hi = __uint_as_float(words[j] & 0xffff0000u) * w;
-          words[j] = pack_bf16(lo, hi);
-        }
-        *reinterpret_cast<uint4*>(dst + ch * 16) = raw;
-      }
+      scaled_row_copy(stage_v(c % kStages), vw_buf(c & 1), row, w);
       fence_proxy_async();
       mbar_arrive(&bar_vw_ready[c & 1]);
     }
