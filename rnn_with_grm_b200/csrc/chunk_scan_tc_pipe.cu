@@ -1,32 +1,39 @@
 // Warp-specialised, pipelined tcgen05 kernel of the linear-memory scan
-// (d_k = d_v = 64, bf16 operands, fp32 state in TMEM, chunks of 128 tokens).
+// (d_k = d_v = 64, bf16 operands, fp32 state in registers, chunks of 128 tokens).
 //
 // Per chunk c, with Q, Kc, Vc the chunk's [128 x 64] tiles and M the carried state:
 //
-//   S  = Q Kc^T                                   128 x 128 x 64   smem x smem
-//   O  = Qs Mb^T           Qs_i = hs * decay^(i+1) q_i,  Mb = bf16(M_{c-1})
-//   M  = decay^len M + Vw^T Kc       Vw_j = coeff * decay^(len-1-j) v_j        (state, TMEM)
-//   O += P Vc              P_ij = hs * coeff * decay^(i-j) S_ij (j <= i)       TMEM x smem
-//   out = O
+//   [S | R] = Q [Kc ; Mb]^T       128 x 192 x 64, one product: S = Q Kc^T, R = Q Mb^T, Mb = bf16(M_{c-1})
+//   U  = Vw^T Kc                  Vw_j = coeff * decay^(len-1-j) v_j       (the chunk's own contribution)
+//   A  = P Vc                     P_ij = hs * coeff * decay^(i-j) S_ij (j <= i)         TMEM x smem
+//   M  = decay^len M + U          fp32 FMA in registers
+//   out_i = hs * decay^(i+1) R_i + A_i                                    fp32, in the epilogue
 //
 // which is the closed form of the reference chunk (grm/core/cuda_ops.py:218-254) with the state
-// carried across chunks as in grm/csrc/grm_cuda.cpp:67-83.  Roles:
+// carried across chunks as in grm/csrc/grm_cuda.cpp:67-83.  No tensor-core product waits for a
+// tensor-core product of the chunk before it except through the state, and the state costs one
+// register FMA and one shared-memory store per chunk: the rest is a pipeline.  Roles:
 //
-//   warp 12      issuer A (one thread): O_c(P part) | S_{c+2} | TMA loads of chunk c+3 (3-stage ring)
-//   warp 13      issuer B (one thread): O_c(state part), M_c  -- the only products on the
-//                recurrence, so that the serial chain is state pass -> 12 MMAs -> state pass
-//   warps 8-11   copy group: Vw_c and Qs_c, the two decay-scaled copies, ahead of the issuer
-//   warps 0-3    compute group 0, chunks 0, 2, 4, ...
-//   warps 4-7    compute group 1, chunks 1, 3, 5, ...
+//   warp 12      issuer A: [S | R]_c; owns the TMEM allocation
+//   warp 13      issuer B: U_c, up to two chunks ahead
+//   warp 14      issuer C: A_c
+//   warp 15      loader: TMA ring of three stages, refilled as soon as a chunk's tiles are dead
+//                (issuers run as whole warps with one elected lane executing the instruction)
+//   warps 8-11   state group: Vw_c, the decay-scaled copy of V; the state, one row per thread in
+//                lanes 0-15 of each warp (the layout of a 64-row accumulator),
+//                M_c = decay^len M_{c-1} + U_c, and its bf16 copy behind the K tile of chunk c+1
+//   warps 0-3    compute group 0: columns 0-63 of S_c, output columns 0-31
+//   warps 4-7    compute group 1: columns 64-127 of S_c, output columns 32-63
 //                each: S_c -> P_c (decay mask, bf16, written back into the TMEM columns of S_c),
-//                      state pass (M_c -> bf16 copy for the next chunk, rescale in TMEM),
-//                      epilogue (O_c -> bf16 -> HBM)
+//                      then the epilogue of chunk c-1 (R, A -> out -> HBM)
 //
-// P never touches shared memory: O += P Vc takes its A operand from TMEM.  TMEM (512 columns):
-// two S/P buffers (one per compute group), two O buffers, the state.  Every hand-off is an
-// mbarrier; a waiter is never more than one phase behind its producer (protocol comment in the
-// kernel) and every wait is bounded: on expiry the CTA-wide abort flag is raised, all roles drain,
-// the error word gets bit 1, TMEM is freed and the kernel returns.
+// P never touches shared memory: A = P Vc takes its left operand from TMEM.  Shared memory holds
+// three stages [q | k | Mb | v] (the state copy sits right behind k so that [Kc ; Mb] is one
+// operand) and two Vw buffers.  TMEM (512 columns): two buffers of 192 columns
+// [S -> P (0-63) , A (64-127) | R (128-191)], used by alternate chunks, and two U buffers.  Every
+// hand-off is an mbarrier; a waiter is never more than one phase behind its producer (protocol
+// comment in the kernel) and every wait is bounded: on expiry the CTA-wide abort flag is raised,
+// all roles drain, the error word gets bit 1, TMEM is freed and the kernel returns.
 #include <cuda.h>
 
 #include <mutex>
@@ -42,35 +49,46 @@ using namespace tc;
 constexpr int kChunk = 128;
 constexpr int kD = 64;                 // d_k == d_v
 constexpr int kStages = 3;
-constexpr int kThreads = 448;          // 14 warps (registers are granted as for 16: 128 per thread)
-constexpr int kCopyWarp0 = 8;          // warps 8-11, one token row per thread
-constexpr int kCopyThreads = 128;
-constexpr int kIssuerA = 12;           // S, P part of O, TMA; also owns the TMEM allocation
-constexpr int kIssuerB = 13;           // state part of O, state update
+constexpr int kThreads = 512;          // 16 warps, 128 registers per thread
+constexpr int kStateWarp0 = 8;         // warps 8-11
+constexpr int kStateThreads = 128;
+constexpr int kIssuerA = 12;           // [S | R]; also owns the TMEM allocation
+constexpr int kIssuerB = 13;           // U
+constexpr int kIssuerC = 14;           // A = P V
+constexpr int kLoader = 15;            // TMA
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0;          // + 128 * group : S (128 cols), then P in cols 0-63 (bf16 pairs)
-constexpr uint32_t kColO = 256;        // + 64 * group  : O
-constexpr uint32_t kColM = 384;        // state: 64 columns, lanes 0-15 of each quarter
+constexpr uint32_t kColBuf = 0;        // + 192 * (c & 1): S (0-127) -> P (0-63, bf16 pairs), A (64-127), R (128-191)
+constexpr uint32_t kBufCols = 192;
+constexpr uint32_t kColA = 64;         // within a buffer
+constexpr uint32_t kColR = 128;        // within a buffer
+constexpr uint32_t kColU = 384;        // + 64 * (c & 1): U, lanes 0-15 of each quarter
 
 constexpr int kTileBytes = kChunk * kD * 2;          // 16 KiB: one [128 x 64] bf16 tile
-constexpr int kStageBytes = 3 * kTileBytes;          // q, k, v
+constexpr int kMbBytes = kD * kD * 2;                // 8 KiB: [64 x 64] bf16
+constexpr int kStageQ = 0;
+constexpr int kStageK = kTileBytes;
+constexpr int kStageMb = 2 * kTileBytes;             // directly behind k
+constexpr int kStageV = 2 * kTileBytes + kMbBytes;
+constexpr int kStageBytes = 3 * kTileBytes + kMbBytes;
+constexpr int kTxBytes = 3 * kTileBytes;             // what TMA delivers per stage
 constexpr int kOffStage = 0;
 constexpr int kOffVw = kStages * kStageBytes;        // two buffers
-constexpr int kOffQs = kOffVw + 2 * kTileBytes;      // two buffers
-constexpr int kOffMb = kOffQs + 2 * kTileBytes;      // [64 x 64] bf16
 // Decay weights of P, reversed (entry m holds weight(d = 127 - m), zero for d < 0) and stored as
 // four copies shifted by 0..3 entries so that any run of 32 weights can be read with aligned
 // 16-byte loads; copies are 264 floats apart, which keeps the eight lanes of a load phase on
 // distinct banks.
 constexpr int kWcopy = 264;
-constexpr int kOffWtab = kOffMb + kD * kD * 2;
+constexpr int kOutBytes = kChunk * 32 * 2;             // 8 KiB: [128 x 32] bf16, one per compute group
+constexpr int kOffOut = kOffVw + 2 * kTileBytes;
+constexpr int kOffWtab = kOffOut + 2 * kOutBytes;
 constexpr int kOffPow = kOffWtab + 4 * kWcopy * 4;   // float[kChunk + 4]: decay^j
 constexpr int kOffBars = kOffPow + (kChunk + 4) * 4;
-constexpr int kNumBars = 24;
+constexpr int kNumBars = 32;
 constexpr int kOffMisc = kOffBars + kNumBars * 8;
 constexpr int kSmemTotal = kOffMisc + 32;
 constexpr int kSmemAlloc = kSmemTotal + 1024;
 static_assert(kSmemAlloc <= 232448, "shared memory plan exceeds 227 KiB");
+static_assert(kStageBytes % 1024 == 0 && kStageMb % 1024 == 0 && kStageV % 1024 == 0, "swizzle atoms are 1 KiB");
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -81,7 +99,8 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { re
 
 __global__ void __launch_bounds__(kThreads, 1)
 linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                           const __grid_constant__ CUtensorMap map_v, ScanParams p, SplitInfo split,
+                           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                           ScanParams p, SplitInfo split,
                            uint32_t* error_word) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -89,13 +108,18 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   float* s_pow = reinterpret_cast<float*>(smem + kOffPow);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   uint64_t* bar_full = bars;              // [3] TMA bytes landed                             (1 + tx)
-  uint64_t* bar_s_done = bars + 6;        // [2] S_c complete                                 (commit)
-  uint64_t* bar_p_ready = bars + 8;       // [2] P_c in TMEM                                  (128)
-  uint64_t* bar_vq_ready = bars + 10;     // [2] Vw_c and Qs_c written                        (128)
-  uint64_t* bar_d_done = bars + 12;       // [2] state part of O_c and M_c complete           (commit)
-  uint64_t* bar_o_done = bars + 14;       // [2] O_c complete                                 (commit)
-  uint64_t* bar_o_free = bars + 16;       // [2] epilogue c has read O_c                      (128)
-  uint64_t* bar_state_ready = bars + 18;  // [1] bf16 state copy + rescaled TMEM state        (128)
+  uint64_t* bar_s_done = bars + 4;        // [2] [S | R]_c complete                           (commit)
+  uint64_t* bar_p_ready = bars + 6;       // [2] P_c in TMEM                                  (256)
+  uint64_t* bar_vw_ready = bars + 8;      // [2] Vw_c written                                 (128)
+  uint64_t* bar_u_done = bars + 10;       // [2] U_c complete                                 (commit)
+  uint64_t* bar_a_done = bars + 12;       // [2] A_c complete                                 (commit)
+  uint64_t* bar_buf_free = bars + 14;     // [2] epilogue c has read R_c and A_c              (256)
+  uint64_t* bar_mb_ready = bars + 16;     // [3] bf16 copy of the state before chunk c        (128)
+  uint64_t* bar_u_free = bars + 20;       // [2] U_c folded into the state                    (128)
+  uint64_t* bar_stage_free = bars + 22;   // [3] U_c and A_c complete: the tiles of chunk c are dead (2)
+  uint64_t* bar_s_read = bars + 26;       // [2] compute group 0 has S block 1 in registers   (128)
+  uint64_t* bar_out_ready = bars + 28;    // [2] group g has written its half of the output tile (128)
+  uint64_t* bar_out_free = bars + 30;     // [2] the store of that half tile has read it      (1)
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 8);
 
@@ -124,16 +148,21 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) {
       mbar_init(&bar_full[i], 1);
+      mbar_init(&bar_mb_ready[i], kStateThreads);
+      mbar_init(&bar_stage_free[i], 2);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_s_done[i], 1);
-      mbar_init(&bar_p_ready[i], 128);
-      mbar_init(&bar_vq_ready[i], kCopyThreads);
-      mbar_init(&bar_d_done[i], 1);
-      mbar_init(&bar_o_done[i], 1);
-      mbar_init(&bar_o_free[i], 128);
+      mbar_init(&bar_p_ready[i], 256);
+      mbar_init(&bar_s_read[i], 128);
+      mbar_init(&bar_out_ready[i], 128);
+      mbar_init(&bar_out_free[i], 1);
+      mbar_init(&bar_vw_ready[i], kStateThreads);
+      mbar_init(&bar_u_done[i], 1);
+      mbar_init(&bar_a_done[i], 1);
+      mbar_init(&bar_buf_free[i], 256);
+      mbar_init(&bar_u_free[i], kStateThreads);
     }
-    mbar_init(bar_state_ready, 128);
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -156,12 +185,8 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
 
-  uint8_t* s_mb = smem + kOffMb;
-  auto stage_q = [&](int s) { return smem + kOffStage + s * kStageBytes; };
-  auto stage_k = [&](int s) { return stage_q(s) + kTileBytes; };
-  auto stage_v = [&](int s) { return stage_q(s) + 2 * kTileBytes; };
-  auto vw_buf = [&](int i) { return smem + kOffVw + i * kTileBytes; };
-  auto qs_buf = [&](int i) { return smem + kOffQs + i * kTileBytes; };
+  auto stage = [&](int c) { return smem + kOffStage + (c % kStages) * kStageBytes; };
+  auto vw_buf = [&](int c) { return smem + kOffVw + (c & 1) * kTileBytes; };
 
 #define GRMX_WAIT(bar, phase)                                        \
   if (!mbar_wait((bar), static_cast<uint32_t>(phase) & 1u, s_abort)) \
@@ -171,313 +196,337 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   // barrier X that belongs to chunk c (phase c/2 of X[c&1], phase c/3 of X[c%3]).  A waiter is
   // never more than one completion behind, because the producer's next completion on the same
   // barrier needs something that comes after the waiter's wait:
-  //   issuer B: O_c(state part), M_c need vq_ready(c)    <- copy group     <- full(c), d_done(c-2)
-  //                                       state_ready(c) <- state pass c-1 <- d_done(c-1)
-  //                                       o_free(c-2)    <- epilogue c-2   <- o_done(c-2)
-  //   issuer A: O_c(P part)          needs p_ready(c)    <- P pass c       <- s_done(c)
-  //                                        d_done(c)     (the state part is accumulated first)
-  //             S_{c+2}              needs o_done(c) (O_c reads its S/P buffer) and full(c+2)
-  //             TMA of chunk c+3     needs o_done(c): every reader of stage c%3 has retired
+  //   loader:   TMA of c    needs stage_free(c-3): one arrival after u_done(c-3) (state group), one
+  //                         after a_done(c-3) (epilogue), which also follows [S | R]_{c-3}
+  //   issuer A: [S | R]_c   needs full(c), mb_ready(c), buf_free(c-2)
+  //   state:    Vw_c        needs full(c) and u_done(c-2) (waited for M_{c-2}, earlier in program order)
+  //             M_c         needs u_done(c); its bf16 copy goes behind the K tile of chunk c+1, whose
+  //                         stage is known to be free because full(c+1) was waited for Vw_{c+1}
+  //   issuer B: U_c         needs vw_ready(c), u_free(c-2)
+  //   issuer C: A_c         needs p_ready(c)
+  //   P pass c  needs s_done(c) (group 1 also s_read(c) before it stores); epilogue c needs a_done(c)
+  // mb_ready has three barriers (X[c%3], phase c/3): mb_ready(c+3) follows Vw_{c+3} in the state
+  // group's program order, hence the TMA of chunk c+3, hence a_done(c) and [S | R]_c, which issuer
+  // A issues after passing mb_ready(c); with two barriers the loads of the prologue would leave a
+  // window.
 
   if (warp == kIssuerA) {
-    // ===================================================================== issuer A + TMA
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc(kChunk, kChunk, 0, 0);
-      constexpr uint32_t idesc_op = make_idesc(kChunk, kD, 0, 1);
-      int loads_issued = 0;
-
-      auto issue_loads = [&](int c) {
-        const int s = c % kStages;
-        mbar_expect_tx(&bar_full[s], kStageBytes);
-        const int t0 = chunk_token0(c_begin + c);
-        tma_load_3d(stage_q(s), &map_q, &bar_full[s], 0, t0, static_cast<int>(b));
-        tma_load_3d(stage_k(s), &map_k, &bar_full[s], 0, t0, static_cast<int>(b));
-        tma_load_3d(stage_v(s), &map_v, &bar_full[s], 0, t0, static_cast<int>(b));
-        loads_issued = c + 1;
-      };
-      auto issue_s = [&](int c) {
-        const int s = c % kStages;
-        const uint64_t dq = smem_desc(smem_u32(stage_q(s)), 16, 1024);
-        const uint64_t dk = smem_desc(smem_u32(stage_k(s)), 16, 1024);
-        const uint32_t d_tmem = tmem_base + kColS + 128u * (c & 1);
+    // ===================================================================== issuer A: [S | R]
+    const uint32_t leader = elect_one();
+    constexpr uint32_t idesc_sr = make_idesc(kChunk, kChunk + kD, 0, 0);
+    for (int c = 0; c < n_chunks; ++c) {
+      GRMX_WAIT(&bar_mb_ready[c % 3], c / 3)
+      GRMX_WAIT(&bar_full[c % kStages], c / kStages)
+      if (c >= 2) GRMX_WAIT(&bar_buf_free[c & 1], c / 2 - 1)
+      tc_fence_after();
+      const uint8_t* st = stage(c);
+      const uint64_t dq = smem_desc(smem_u32(st + kStageQ), 16, 1024);
+      const uint64_t dkm = smem_desc(smem_u32(st + kStageK), 16, 1024);   // 128 rows of k, then 64 of Mb
+      const uint32_t d_tmem = tmem_base + kColBuf + kBufCols * (c & 1);
 #pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          tc_mma_bf16(d_tmem, desc_add(dq, kk * 32), desc_add(dk, kk * 32), idesc_s, kk > 0);
-        }
-        tc_commit(&bar_s_done[c & 1]);
-      };
-
-      for (int c = 0; c < n_chunks && c < kStages; ++c) issue_loads(c);
-      do {
-        GRMX_WAIT(&bar_full[0], 0)
-        tc_fence_after();
-        issue_s(0);
-        if (n_chunks > 1) {
-          GRMX_WAIT(&bar_full[1], 0)
-          tc_fence_after();
-          issue_s(1);
-        }
-        for (int c = 0; c < n_chunks; ++c) {
-          const int s = c % kStages;
-          const int g = c & 1;
-          GRMX_WAIT(&bar_p_ready[g], c / 2)
-          GRMX_WAIT(&bar_d_done[g], c / 2)
-          tc_fence_after();
-          {
-            const uint64_t dv_mn = smem_desc(smem_u32(stage_v(s)), kTileBytes, 1024);
-            const uint32_t p_tmem = tmem_base + kColS + 128u * g;   // 16 tokens of P = 8 columns
-            const uint32_t o_tmem = tmem_base + kColO + 64u * g;
-#pragma unroll
-            for (int kk = 0; kk < kChunk / 16; ++kk) {
-              tc_mma_bf16_ts(o_tmem, p_tmem + 8u * kk, desc_add(dv_mn, kk * 2048), idesc_op, 1u);
-            }
-            tc_commit(&bar_o_done[g]);
-          }
-          if (c + 2 < n_chunks) {
-            GRMX_WAIT(&bar_full[(c + 2) % kStages], (c + 2) / kStages)
-            GRMX_WAIT(&bar_o_done[g], c / 2)       // O_c has consumed P_c: the S/P buffer is free
-            tc_fence_after();
-            issue_s(c + 2);
-            if (c + 3 < n_chunks) issue_loads(c + 3);   // stage c % 3: all its readers retired with O_c
-          }
-        }
-      } while (false);
-      if (*s_abort) {
-        // let the copies still in flight land before the shared memory is released
-        for (int c = loads_issued > kStages ? loads_issued - kStages : 0; c < loads_issued; ++c) {
-          mbar_wait_quiet(&bar_full[c % kStages], (c / kStages) & 1);
-        }
+      for (int kk = 0; kk < kD / 16; ++kk) {
+        tc_mma_bf16_if(leader, d_tmem, desc_add(dq, kk * 32), desc_add(dkm, kk * 32), idesc_sr, kk > 0);
+      }
+      tc_commit_if(leader, &bar_s_done[c & 1]);
+    }
+  } else if (warp == kLoader) {
+    // ===================================================================== loader: TMA ring
+    const uint32_t leader = elect_one();
+    int loads_issued = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+      if (c >= kStages) GRMX_WAIT(&bar_stage_free[c % kStages], c / kStages - 1)
+      uint8_t* st = stage(c);
+      uint64_t* bar = &bar_full[c % kStages];
+      mbar_expect_tx_if(leader, bar, kTxBytes);
+      const int t0 = chunk_token0(c_begin + c);
+      tma_load_3d_if(leader, st + kStageQ, &map_q, bar, 0, t0, static_cast<int>(b));
+      tma_load_3d_if(leader, st + kStageK, &map_k, bar, 0, t0, static_cast<int>(b));
+      tma_load_3d_if(leader, st + kStageV, &map_v, bar, 0, t0, static_cast<int>(b));
+      loads_issued = c + 1;
+    }
+    if (*s_abort) {
+      // let the copies still in flight land before the shared memory is released
+      for (int c = loads_issued > kStages ? loads_issued - kStages : 0; c < loads_issued; ++c) {
+        mbar_wait_quiet(&bar_full[c % kStages], (c / kStages) & 1);
       }
     }
   } else if (warp == kIssuerB) {
-    // ===================================================================== issuer B
-    if (lane == 0) {
-      constexpr uint32_t idesc_oq = make_idesc(kChunk, kD, 0, 0);
-      constexpr uint32_t idesc_m = make_idesc(kD, kD, 1, 1);
-      const uint64_t desc_mb = smem_desc(smem_u32(s_mb), 16, 1024);
-      for (int c = 0; c < n_chunks; ++c) {
-        const int s = c % kStages;
-        const int g = c & 1;
-        GRMX_WAIT(&bar_vq_ready[g], c / 2)
-        if (c >= 2) GRMX_WAIT(&bar_o_free[g], c / 2 - 1)
-        GRMX_WAIT(bar_state_ready, c)
-        tc_fence_after();
-        const uint64_t dqs = smem_desc(smem_u32(qs_buf(g)), 16, 1024);
-        const uint64_t dk_mn = smem_desc(smem_u32(stage_k(s)), kTileBytes, 1024);
-        const uint64_t dvw = smem_desc(smem_u32(vw_buf(g)), kTileBytes, 1024);
-        const uint32_t o_tmem = tmem_base + kColO + 64u * g;
-#pragma unroll
-        for (int kk = 0; kk < kChunk / 16; ++kk) {
-          tc_mma_bf16(tmem_base + kColM, desc_add(dvw, kk * 2048), desc_add(dk_mn, kk * 2048), idesc_m, 1u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < kD / 16; ++kk) {
-          tc_mma_bf16(o_tmem, desc_add(dqs, kk * 32), desc_add(desc_mb, kk * 32), idesc_oq, kk > 0);
-        }
-        tc_commit(&bar_d_done[g]);
-      }
-    }
-  } else if (warp >= kCopyWarp0) {
-    // ===================================================================== copy group (warps 8-11)
-    const int row = tid - kCopyWarp0 * 32;
-    const int step = rev ? kChunk - 1 - row : row;
+    // ===================================================================== issuer B: U
+    const uint32_t leader = elect_one();
+    constexpr uint32_t idesc_u = make_idesc(kD, kD, 1, 1);
     for (int c = 0; c < n_chunks; ++c) {
-      GRMX_WAIT(&bar_full[c % kStages], c / kStages)
-      if (c >= 2) GRMX_WAIT(&bar_d_done[c & 1], c / 2 - 1)
+      GRMX_WAIT(&bar_vw_ready[c & 1], c / 2)
+      if (c >= 2) GRMX_WAIT(&bar_u_free[c & 1], c / 2 - 1)
+      tc_fence_after();
+      const uint64_t dvw = smem_desc(smem_u32(vw_buf(c)), kTileBytes, 1024);
+      const uint64_t dk_mn = smem_desc(smem_u32(stage(c) + kStageK), kTileBytes, 1024);
+      const uint32_t u_tmem = tmem_base + kColU + 64u * (c & 1);
+#pragma unroll
+      for (int kk = 0; kk < kChunk / 16; ++kk) {
+        tc_mma_bf16_if(leader, u_tmem, desc_add(dvw, kk * 2048), desc_add(dk_mn, kk * 2048), idesc_u, kk > 0);
+      }
+      tc_commit_if(leader, &bar_u_done[c & 1]);
+    }
+  } else if (warp == kIssuerC) {
+    // ===================================================================== issuer C: A = P V
+    const uint32_t leader = elect_one();
+    constexpr uint32_t idesc_a = make_idesc(kChunk, kD, 0, 1);
+    for (int c = 0; c < n_chunks; ++c) {
+      GRMX_WAIT(&bar_p_ready[c & 1], c / 2)
+      tc_fence_after();
+      const uint64_t dv_mn = smem_desc(smem_u32(stage(c) + kStageV), kTileBytes, 1024);
+      const uint32_t buf = tmem_base + kColBuf + kBufCols * (c & 1);    // P: 16 tokens = 8 columns
+#pragma unroll
+      for (int kk = 0; kk < kChunk / 16; ++kk) {
+        tc_mma_bf16_ts_if(leader, buf + kColA, buf + 8u * kk, desc_add(dv_mn, kk * 2048), idesc_a, kk > 0);
+      }
+      tc_commit_if(leader, &bar_a_done[c & 1]);
+    }
+  } else if (warp >= kStateWarp0) {
+    // ===================================================================== state group (warps 8-11)
+    const int row = tid - kStateWarp0 * 32;   // token row of the copy
+    const int step = rev ? kChunk - 1 - row : row;
+    const int quarter = warp - kStateWarp0;
+    const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const bool owns_row = lane < 16;          // 64-row accumulator: lanes 0-15 of each quarter
+    const int state_row = quarter * 16 + (lane & 15);
+    float m[kD];                              // state row, fp32
+
+    auto write_mb = [&](int c) {              // the state before chunk c, behind that chunk's K tile
+      uint8_t* mrow = stage(c) + kStageMb + state_row * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        uint4 w;
+        w.x = pack_bf16(m[ch * 8 + 0], m[ch * 8 + 1]);
+        w.y = pack_bf16(m[ch * 8 + 2], m[ch * 8 + 3]);
+        w.z = pack_bf16(m[ch * 8 + 4], m[ch * 8 + 5]);
+        w.w = pack_bf16(m[ch * 8 + 6], m[ch * 8 + 7]);
+        *reinterpret_cast<uint4*>(mrow + ((ch ^ (state_row & 7)) * 16)) = w;
+      }
+    };
+    auto copy_chunk = [&](int c) {
       const int g = c_begin + c;
       const int len = chunk_len(g);
-      const bool live = step < len;
-      const float w_v = live ? p.update_coeff * s_pow[len - 1 - step] : 0.0f;
-      const float w_q = live ? p.hidden_scale * s_pow[step + 1 - first_offset(g)] : 0.0f;
-      scaled_row_copy(stage_v(c % kStages), vw_buf(c & 1), row, w_v);
-      scaled_row_copy(stage_q(c % kStages), qs_buf(c & 1), row, w_q);
+      const float w_v = step < len ? p.update_coeff * s_pow[len - 1 - step] : 0.0f;
+      scaled_row_copy<4>(stage(c) + kStageV, vw_buf(c), row, w_v);
       fence_proxy_async();
-      mbar_arrive(&bar_vq_ready[c & 1]);
+      mbar_arrive(&bar_vw_ready[c & 1]);
+    };
+
+    // state at the start of this CTA's chunks
+    {
+      const float* m_in = static_cast<const float*>(p.memory_in) + b * kD * kD;
+      const float* src = m_in + state_row * p.m_row_stride;
+      const bool vec = p.m_col_stride == 1 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+      if (owns_row && vec) {
+#pragma unroll
+        for (int j = 0; j < kD / 4; ++j) {
+          const float4 x = __ldg(reinterpret_cast<const float4*>(src) + j);
+          m[4 * j] = x.x; m[4 * j + 1] = x.y; m[4 * j + 2] = x.z; m[4 * j + 3] = x.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kD; ++j) m[j] = owns_row ? src[j * p.m_col_stride] : 0.0f;
+      }
+      // pieces before this one: M <- decay^(tokens of piece q - offset) M + partial_q
+      for (int q = 0; q < piece; ++q) {
+        const int q_tokens = min(split.chunks_per_piece * kChunk, T - q * split.chunks_per_piece * kChunk);
+        const float gq = powf(p.decay, static_cast<float>(q_tokens - first_offset(q * split.chunks_per_piece)));
+        if (owns_row) {
+          const float4* part = reinterpret_cast<const float4*>(
+              split.partials + ((b * (split.pieces - 1) + q) * kD + state_row) * kD);
+#pragma unroll
+          for (int j = 0; j < kD / 4; ++j) {
+            const float4 x = __ldg(part + j);
+            m[4 * j] = fmaf(gq, m[4 * j], x.x);
+            m[4 * j + 1] = fmaf(gq, m[4 * j + 1], x.y);
+            m[4 * j + 2] = fmaf(gq, m[4 * j + 2], x.z);
+            m[4 * j + 3] = fmaf(gq, m[4 * j + 3], x.w);
+          }
+        }
+      }
+      if (owns_row) write_mb(0);              // TMA never writes this part of a stage
+      fence_proxy_async();
+      mbar_arrive(&bar_mb_ready[0]);          // completion 0: the state before chunk 0
     }
+
+    do {
+      GRMX_WAIT(&bar_full[0], 0)
+      copy_chunk(0);
+      if (n_chunks > 1) {
+        GRMX_WAIT(&bar_full[1], 0)
+        copy_chunk(1);
+      }
+      for (int c = 0; c < n_chunks; ++c) {
+        const bool last = c + 1 == n_chunks;
+        // ---- M_c = decay^len M_{c-1} + U_c ----
+        GRMX_WAIT(&bar_u_done[c & 1], c / 2)
+        if (row == 0) mbar_arrive(&bar_stage_free[c % kStages]);
+        tc_fence_after();
+        {
+          const float carry = s_pow[chunk_len(c_begin + c) - first_offset(c_begin + c)];
+#pragma unroll
+          for (int part = 0; part < 4; ++part) {
+            float u[16];
+            tc_ld16(tmem_lane + kColU + 64u * (c & 1) + 16u * part, u);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) m[16 * part + j] = fmaf(carry, m[16 * part + j], u[j]);
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&bar_u_free[c & 1]);
+        if (!last) {
+          if (owns_row) write_mb(c + 1);
+          fence_proxy_async();
+          mbar_arrive(&bar_mb_ready[(c + 1) % 3]);
+        } else if (owns_row && p.memory_out != nullptr && piece + 1 == split.pieces) {
+          float* m_out = static_cast<float*>(p.memory_out) + b * kD * kD + state_row * kD;
+#pragma unroll
+          for (int j = 0; j < kD; j += 4) {
+            float4 o;
+            o.x = m[j] * p.memory_out_scale;
+            o.y = m[j + 1] * p.memory_out_scale;
+            o.z = m[j + 2] * p.memory_out_scale;
+            o.w = m[j + 3] * p.memory_out_scale;
+            *reinterpret_cast<float4*>(m_out + j) = o;
+          }
+        }
+        // ---- Vw of chunk c+2 into the buffer that U_c has read ----
+        if (c + 2 < n_chunks) {
+          GRMX_WAIT(&bar_full[(c + 2) % kStages], (c + 2) / kStages)
+          copy_chunk(c + 2);
+        }
+      }
+    } while (false);
   } else {
     // ===================================================================== compute groups (warps 0-7)
-    const int g = warp >> 2;                  // group 0: even chunks, group 1: odd chunks
+    // Both groups work on every chunk and split it by columns: group g turns the 32-column blocks
+    // 2g and 2g+1 of S into P, and writes the output columns 32g .. 32g+31.  Warp w of a group owns
+    // rows 32w .. 32w+31, so blocks above block w (below it in a reverse scan) are all zero.
+    // P block blk (16 packed columns) lands on S columns 16*blk .. 16*blk+15: group 0 overwrites
+    // what it has read itself, group 1 overwrites S block 1, which group 0 reads, and waits for
+    // s_read(c) before it stores.
+    const int g = warp >> 2;
     const int quarter = warp & 3;
     const int row = tid & 127;                // token row within the chunk == TMEM lane
     const int step = rev ? kChunk - 1 - row : row;
-    const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t s_row = tmem_lane + kColS + 128u * g;
-    const uint32_t o_row = tmem_lane + kColO + 64u * g;
-    const bool owns_row = lane < 16;          // M = 64 accumulator: lanes 0-15 of each quarter
-    const int state_row = quarter * 16 + (lane & 15);
-    // decay applied to the carried state over chunk c (the state in TMEM is kept pre-scaled by it)
-    auto carry_of = [&](int c) { return s_pow[chunk_len(c_begin + c) - first_offset(c_begin + c)]; };
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kColBuf;
+    const bool nz0 = rev ? 2 * g >= quarter : 2 * g <= quarter;            // block 2g is not all zero
+    const bool nz1 = rev ? 2 * g + 1 >= quarter : 2 * g + 1 <= quarter;    // block 2g+1
+    const int m_first = 127 - row + 64 * g;   // reversed-table index of column 64g
 
-    auto write_mb = [&](const float (&v)[32], int c0) {
-      uint8_t* mrow = s_mb + state_row * 128;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        const int chunk16 = (c0 / 8 + ch) ^ (state_row & 7);
-        uint4 w;
-        w.x = pack_bf16(v[ch * 8 + 0], v[ch * 8 + 1]);
-        w.y = pack_bf16(v[ch * 8 + 2], v[ch * 8 + 3]);
-        w.z = pack_bf16(v[ch * 8 + 4], v[ch * 8 + 5]);
-        w.w = pack_bf16(v[ch * 8 + 6], v[ch * 8 + 7]);
-        *reinterpret_cast<uint4*>(mrow + chunk16 * 16) = w;
-      }
-    };
-
-    if (g == 0) {
-      // state at the start of this CTA's chunks -> bf16 copy + TMEM (pre-scaled by the first carry)
-      const float* m_in = static_cast<const float*>(p.memory_in) + b * kD * kD;
-      const bool dense = p.m_col_stride == 1;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kD; c0 += 32) {
-        float v[32];
-        if (owns_row && dense) {
-          const float4* src = reinterpret_cast<const float4*>(m_in + state_row * p.m_row_stride + c0);
-          const bool vec = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (vec) {
-              const float4 x = __ldg(src + j);
-              v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
-            } else {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) v[4 * j + e] = m_in[state_row * p.m_row_stride + c0 + 4 * j + e];
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = owns_row ? m_in[state_row * p.m_row_stride + (c0 + j) * p.m_col_stride] : 0.0f;
-          }
+    for (int c = 0; c <= n_chunks; ++c) {
+      if (c < n_chunks) {
+        // ---- P pass: S_c -> P_c in place ----
+        const uint32_t buf_row = lane_base + kBufCols * (c & 1);
+        GRMX_WAIT(&bar_s_done[c & 1], c / 2)
+        tc_fence_after();
+        uint32_t sv0[32], sv1[32], pk[16];
+        if (nz0) tc_ld32_async(buf_row + 64u * g, sv0);
+        if (nz1) tc_ld32_async(buf_row + 64u * g + 32u, sv1);
+        tc_wait_ld();
+        if (g == 0) {
+          tc_fence_before();
+          mbar_arrive(&bar_s_read[c & 1]);
         }
-        // pieces before this one: M <- decay^(tokens of piece q - offset) M + partial_q
-        for (int q = 0; q < piece; ++q) {
-          const int q_tokens = min(split.chunks_per_piece * kChunk, T - q * split.chunks_per_piece * kChunk);
-          const float gq = powf(p.decay, static_cast<float>(q_tokens - first_offset(q * split.chunks_per_piece)));
-          if (owns_row) {
-            const float4* part = reinterpret_cast<const float4*>(
-                split.partials + ((b * (split.pieces - 1) + q) * kD + state_row) * kD + c0);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 x = __ldg(part + j);
-              v[4 * j] = fmaf(gq, v[4 * j], x.x);
-              v[4 * j + 1] = fmaf(gq, v[4 * j + 1], x.y);
-              v[4 * j + 2] = fmaf(gq, v[4 * j + 2], x.z);
-              v[4 * j + 3] = fmaf(gq, v[4 * j + 3], x.w);
-            }
-          }
-        }
-        if (owns_row) write_mb(v, c0);
-        const float carry = carry_of(0);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] *= carry;
-        tc_st32(tmem_lane + kColM + c0, v);
-      }
-      fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive(bar_state_ready);   // completion 0
-    }
-
-    for (int c = g; c < n_chunks; c += 2) {
-      const bool last = c + 1 == n_chunks;
-      // ---- P pass: S_c -> P_c in place ----
-      // Warp w owns rows 32w..32w+31, so 32-column blocks above block w (below it in a reverse
-      // scan) are all zero.  P block b (16 packed columns) overwrites the S columns 16b..16b+15,
-      // which belong to S blocks 0 and 1: those two are in registers before anything is stored.
-      GRMX_WAIT(&bar_s_done[g], c / 2)
-      tc_fence_after();
-#pragma unroll
-      for (int blk = 0; blk < 4; ++blk) {
-        // P block blk lands on S columns 16*blk..16*blk+15, i.e. inside S block blk/2, which has been
-        // read by the time it is overwritten (blocks are visited in increasing order)
-        uint32_t pk[16];
-        if (rev ? blk >= quarter : blk <= quarter) {
-          uint32_t sv[32];
-          tc_ld32_async(s_row + 32u * blk, sv);
-          const int m0 = 127 - row + 32 * blk;            // reversed-table index of column 32*blk
+        if (nz0) {
+          const int m0 = m_first;
           const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
-          tc_wait_ld();
 #pragma unroll
           for (int t = 0; t < 8; ++t) {
             const float4 w4 = wv[t];
-            pk[2 * t] = pack_bf16(__uint_as_float(sv[4 * t]) * w4.x, __uint_as_float(sv[4 * t + 1]) * w4.y);
-            pk[2 * t + 1] = pack_bf16(__uint_as_float(sv[4 * t + 2]) * w4.z, __uint_as_float(sv[4 * t + 3]) * w4.w);
+            pk[2 * t] = pack_bf16(__uint_as_float(sv0[4 * t]) * w4.x, __uint_as_float(sv0[4 * t + 1]) * w4.y);
+            pk[2 * t + 1] = pack_bf16(__uint_as_float(sv0[4 * t + 2]) * w4.z, __uint_as_float(sv0[4 * t + 3]) * w4.w);
           }
         } else {
 #pragma unroll
           for (int t = 0; t < 16; ++t) pk[t] = 0u;
         }
-        tc_st16_async(s_row + 16u * blk, pk);
-      }
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(&bar_p_ready[g]);
-
-      // ---- state pass: M_c is complete ----
-      GRMX_WAIT(&bar_d_done[g], c / 2)
-      tc_fence_after();
-      {
-        float* m_out = (last && p.memory_out != nullptr && piece + 1 == split.pieces)
-                           ? static_cast<float*>(p.memory_out) + b * kD * kD
-                           : nullptr;
-        const float carry = last ? 0.0f : carry_of(c + 1);
-#pragma unroll 1
-        for (int c0 = 0; c0 < kD; c0 += 32) {
-          float v[32];
-          tc_ld32(tmem_lane + kColM + c0, v);
-          if (last) {
-            if (owns_row && m_out != nullptr) {
+        if (g == 1) {
+          GRMX_WAIT(&bar_s_read[c & 1], c / 2)
+        }
+        tc_st16_async(buf_row + 32u * g, pk);
+        if (nz1) {
+          const int m0 = m_first + 32;
+          const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o;
-                o.x = v[j] * p.memory_out_scale;
-                o.y = v[j + 1] * p.memory_out_scale;
-                o.z = v[j + 2] * p.memory_out_scale;
-                o.w = v[j + 3] * p.memory_out_scale;
-                *reinterpret_cast<float4*>(m_out + state_row * kD + c0 + j) = o;
-              }
-            }
-          } else {
-            if (owns_row) write_mb(v, c0);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= carry;
-            tc_st32(tmem_lane + kColM + c0, v);
+          for (int t = 0; t < 8; ++t) {
+            const float4 w4 = wv[t];
+            pk[2 * t] = pack_bf16(__uint_as_float(sv1[4 * t]) * w4.x, __uint_as_float(sv1[4 * t + 1]) * w4.y);
+            pk[2 * t + 1] = pack_bf16(__uint_as_float(sv1[4 * t + 2]) * w4.z, __uint_as_float(sv1[4 * t + 3]) * w4.w);
           }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 16; ++t) pk[t] = 0u;
         }
-        if (!last) {
-          fence_proxy_async();
-          tc_fence_before();
-          mbar_arrive(bar_state_ready);   // completion c + 1
-        }
+        tc_st16_async(buf_row + 32u * g + 16u, pk);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bar_p_ready[c & 1]);
       }
-
-      // ---- epilogue: O_c -> bf16 -> HBM ----
-      GRMX_WAIT(&bar_o_done[g], c / 2)
-      tc_fence_after();
-      {
-        const bool row_live = step < chunk_len(c_begin + c);
+      if (c >= 1) {
+        // ---- epilogue of chunk c-1: out_i = hs * decay^(i+1) R_i + A_i -> bf16 -> HBM ----
+        const int e = c - 1;
+        const uint32_t buf_row = lane_base + kBufCols * (e & 1);
+        GRMX_WAIT(&bar_a_done[e & 1], e / 2)
+        if (tid == 0) mbar_arrive(&bar_stage_free[e % kStages]);
+        tc_fence_after();
+        const int ge = c_begin + e;
+        const bool row_live = step < chunk_len(ge);
+        const float r_scale = row_live ? p.hidden_scale * s_pow[step + 1 - first_offset(ge)] : 0.0f;
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.hidden_out) +
-                             (b * p.T + static_cast<int64_t>(chunk_token0(c_begin + c)) + row) * kD;
-        uint32_t o[2][32];
-        tc_ld32_async(o_row, o[0]);
-        tc_ld32_async(o_row + 32u, o[1]);
+                             (b * p.T + static_cast<int64_t>(chunk_token0(ge)) + row) * kD + 32 * g;
+        uint32_t av[32], rv[32];
+        tc_ld32_async(buf_row + kColA + 32u * g, av);
+        tc_ld32_async(buf_row + kColR + 32u * g, rv);
         tc_wait_ld();
         tc_fence_before();
-        mbar_arrive(&bar_o_free[g]);     // the values are in registers: the O buffer may be reused
-        if (row_live) {
+        mbar_arrive(&bar_buf_free[e & 1]);   // the values are in registers: the buffer may be reused
+        // The half tile goes out as one TMA store from shared memory (plain 16-byte stores at a
+        // 128-byte stride cost the load/store unit one line per lane).  A store may not start at a
+        // negative token, which the short last chunk of a reverse scan does: that one is written
+        // with plain stores.  The hand-offs below run for every chunk so that phases stay e.
+        const int t0 = chunk_token0(ge);
+        const bool by_tma = t0 >= 0;
+        uint8_t* s_out = smem + kOffOut + g * kOutBytes;
+        if (e >= 1) {
+          if (row == 0) {
+            bulk_wait_read();
+            mbar_arrive(&bar_out_free[g]);
+          }
+          GRMX_WAIT(&bar_out_free[g], e - 1)
+        }
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+        for (int ch = 0; ch < 4; ++ch) {
+          float o[8];
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-              uint4 w;
-              w.x = pack_bf16(__uint_as_float(o[h][ch * 8 + 0]), __uint_as_float(o[h][ch * 8 + 1]));
-              w.y = pack_bf16(__uint_as_float(o[h][ch * 8 + 2]), __uint_as_float(o[h][ch * 8 + 3]));
-              w.z = pack_bf16(__uint_as_float(o[h][ch * 8 + 4]), __uint_as_float(o[h][ch * 8 + 5]));
-              w.w = pack_bf16(__uint_as_float(o[h][ch * 8 + 6]), __uint_as_float(o[h][ch * 8 + 7]));
-              *reinterpret_cast<uint4*>(out + 32 * h + ch * 8) = w;
-            }
+          for (int i = 0; i < 8; ++i) {
+            o[i] = fmaf(r_scale, __uint_as_float(rv[ch * 8 + i]), __uint_as_float(av[ch * 8 + i]));
+          }
+          uint4 w;
+          w.x = pack_bf16(o[0], o[1]);
+          w.y = pack_bf16(o[2], o[3]);
+          w.z = pack_bf16(o[4], o[5]);
+          w.w = pack_bf16(o[6], o[7]);
+          if (by_tma) {
+            // 64-byte rows, 64-byte swizzle: 16-byte piece j of row r sits at position j ^ ((r >> 1) & 3)
+            *reinterpret_cast<uint4*>(s_out + row * 64 + ((ch ^ ((row >> 1) & 3)) * 16)) = w;
+          } else if (row_live) {
+            *reinterpret_cast<uint4*>(out + ch * 8) = w;
+          }
+        }
+        fence_proxy_async();
+        mbar_arrive(&bar_out_ready[g]);
+        if (row == 0) {
+          GRMX_WAIT(&bar_out_ready[g], e)
+          if (by_tma) {
+            tma_store_3d(s_out, &map_o, 32 * g, t0, static_cast<int>(b));
+            bulk_commit();
           }
         }
       }
     }
+    if (row == 0) bulk_wait_read();   // the last store still reads shared memory
   }
 #undef GRMX_WAIT
 
@@ -513,13 +562,13 @@ int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaSt
     return fail(GRMX_ERR_LAUNCH, "tcgen05 scan: cannot reserve %d bytes of shared memory: %s", kSmemAlloc,
                 cudaGetErrorString(attr_status));
   }
-  CUtensorMap map_q, map_k, map_v;
+  CUtensorMap map_q, map_k, map_v, map_o;
   if (!make_token_map(&map_q, p.queries, p.B, p.T, kD) || !make_token_map(&map_k, p.keys, p.B, p.T, kD) ||
-      !make_token_map(&map_v, p.values, p.B, p.T, kD)) {
+      !make_token_map(&map_v, p.values, p.B, p.T, kD) || !make_token_half_map(&map_o, p.hidden_out, p.B, p.T, kD)) {
     return fail(GRMX_ERR_LAUNCH, "tcgen05 scan: cuTensorMapEncodeTiled failed");
   }
   linear_scan_tc_pipe_kernel<<<static_cast<unsigned>(p.B * split.pieces), kThreads, kSmemAlloc, stream>>>(
-      map_q, map_k, map_v, p, split, device_error_word_ptr());
+      map_q, map_k, map_v, map_o, p, split, device_error_word_ptr());
   return check_launch("linear_scan_tcgen05_pipe");
 }
 

@@ -77,6 +77,18 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+// Tile store shared -> global through a tensor map, as a bulk async-group of the issuing thread
+__device__ __forceinline__ void tma_store_3d(const void* src, const CUtensorMap* map, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(map)),
+      "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all bulk groups of this thread have finished reading their shared-memory source
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t accumulate) {
   asm volatile(
@@ -107,21 +119,106 @@ __device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem,
       : "memory");
 }
 
+// ---- issue from warp-uniform code ----
+// The whole warp runs the issuing loop (waits, descriptor arithmetic) and one elected lane
+// executes the instruction.  With the control flow uniform the compiler can keep descriptors and
+// addresses in uniform registers, which the tensor-core and TMA instructions take directly; in a
+// single-lane branch every operand has to be moved there first, which roughly halves the rate at
+// which small products can be issued.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred;
+}
+
+__device__ __forceinline__ void tc_mma_bf16_if(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_bf16_ts_if(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_commit_if(uint32_t leader, uint64_t* bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}" ::"r"(smem_u32(bar)),
+      "r"(leader)
+      : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx_if(uint32_t leader, uint64_t* bar, uint32_t bytes) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t"
+      "}" ::"r"(smem_u32(bar)),
+      "r"(bytes), "r"(leader)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_if(uint32_t leader, void* dst, const CUtensorMap* map, uint64_t* bar,
+                                               int x, int y, int z) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %6, 0;\n\t"
+      "@q cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];\n\t"
+      "}" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(leader)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// 32 columns of this thread's TMEM lane, asynchronous: follow with tc_wait_ld() before use
-__device__ __forceinline__ void tc_ld32_async(uint32_t taddr, uint32_t (&r)[32]) {
+// 16 columns of this thread's TMEM lane, asynchronous: follow with tc_wait_ld() before use.
+// Loads are kept at 16 columns per instruction: measured on B200, .x16 loads of different warps
+// proceed in parallel (about 20 cycles each), while .x32 and wider loads are served one warp at a
+// time at about 57 bytes per clock for the whole SM.
+__device__ __forceinline__ void tc_ld16_async(uint32_t taddr, uint32_t* r) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+
+// 32 columns of this thread's TMEM lane (two 16-column loads), asynchronous
+__device__ __forceinline__ void tc_ld32_async(uint32_t taddr, uint32_t (&r)[32]) {
+  tc_ld16_async(taddr, &r[0]);
+  tc_ld16_async(taddr + 16u, &r[16]);
 }
 
 // 32 columns to this thread's TMEM lane, asynchronous: follow with tc_wait_st()
@@ -147,19 +244,25 @@ __device__ __forceinline__ void tc_st16_async(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 
+// 16 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // 32 consecutive fp32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
+  tc_ld32_async(taddr, r);
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
@@ -219,23 +322,28 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // elements, which matters because these copies are the largest block of plain instructions in
 // the kernel.  The 16-byte pieces of a row are visited in an order rotated by the row index so
 // that eight neighbouring rows touch eight different bank groups.
+// kBatch of the eight pieces are held in registers at a time (8: one round trip; 4: half the registers).
+template <int kBatch = 8>
 __device__ __forceinline__ void scaled_row_copy(const uint8_t* src_tile, uint8_t* dst_tile, int row, float w) {
   const uint8_t* src = src_tile + row * 128;
   uint8_t* dst = dst_tile + row * 128;
   const __nv_bfloat162 w2 = __float2bfloat162_rn(w);
-  // all eight loads first: source and destination could alias as far as the compiler knows, and
-  // a load-store-load-store sequence would serialise on the shared-memory latency
-  uint4 raw[8];
+  // all loads of a batch first: source and destination could alias as far as the compiler knows,
+  // and a load-store-load-store sequence would serialise on the shared-memory latency
 #pragma unroll
-  for (int i = 0; i < 8; ++i) raw[i] = *reinterpret_cast<const uint4*>(src + ((i + row) & 7) * 16);
+  for (int i0 = 0; i0 < 8; i0 += kBatch) {
+    uint4 raw[kBatch];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw[i]);
+    for (int i = 0; i < kBatch; ++i) raw[i] = *reinterpret_cast<const uint4*>(src + ((i0 + i + row) & 7) * 16);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) pairs[j] = __hmul2(pairs[j], w2);
+    for (int i = 0; i < kBatch; ++i) {
+      __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pairs[j] = __hmul2(pairs[j], w2);
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) *reinterpret_cast<uint4*>(dst + ((i0 + i + row) & 7) * 16) = raw[i];
   }
-#pragma unroll
-  for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(dst + ((i + row) & 7) * 16) = raw[i];
 }
 
 // ---- host helpers (defined in chunk_scan_tc.cu) ----
@@ -248,6 +356,8 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 EncodeTiledFn encode_tiled_fn();
 // 3-D map over a dense [B, T, D] bf16 tensor: box = 64 features x 128 tokens x 1 row, 128-byte swizzle
 bool make_token_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, int64_t D);
+// the same tensor as a store target: box = 32 features x 128 tokens x 1 row, 64-byte swizzle
+bool make_token_half_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, int64_t D);
 bool device_is_sm100();
 
 }  // namespace tc
