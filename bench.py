@@ -137,6 +137,40 @@ def time_launches(fn, steps, warmup, before_timed=None):
     return events[0].elapsed_time(events[steps]), per, (t0, t1)
 
 
+def time_graph(fn, steps, warmup, before_timed=None):
+    """Device time of `steps` calls of fn(i, stream) replayed as ONE CUDA graph.
+
+    The calls are enqueued once, under stream capture, and the timed region is a single graph
+    launch bracketed by CUDA events on the launching stream: what is measured is the GPU
+    executing the steps back to back, not the host enqueueing them (on a slow host core a C-ABI
+    call plus its tensor-map encodes costs about as much as the kernels take to run).
+    Warm-up: `warmup` eager calls, then one untimed replay of the whole graph.
+    """
+    for i in range(warmup):
+        fn(i, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            handle = torch.cuda.current_stream().cuda_stream
+            for i in range(steps):
+                fn(warmup + i, handle)
+        graph.replay()
+        torch.cuda.synchronize()
+        if before_timed is not None:
+            before_timed()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(side)
+        graph.replay()
+        e1.record(side)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+    total = e0.elapsed_time(e1)
+    return total, [total / steps] * steps, (t0, t1)
+
+
 def run_engine(args, rank, world, device):
     from rnn_with_grm_b200 import cabi, cuda_ops
 
@@ -154,12 +188,11 @@ def run_engine(args, rank, world, device):
         sets.append((k, v, q, torch.empty(rows, T, V, device=device, dtype=torch.bfloat16)))
     m_in = torch.zeros(rows, V, K, device=device, dtype=torch.float32)
     m_out = torch.empty_like(m_in)
-    stream = torch.cuda.current_stream().cuda_stream
     # workspace that lets the kernel cut the 64 rows along T so that they fill the GPU
     scratch_bytes = int(lib.grmx_chunk_scan_scratch_bytes(rows, T, K, V, cabi.BF16, cabi.F32))
     scratch = torch.empty(max(scratch_bytes, 16), device=device, dtype=torch.uint8)
 
-    def step(i):
+    def step(i, stream):
         k, v, q, o = sets[i % n_sets]
         cabi.check(lib.grmx_chunk_scan_fwd_ws(k.data_ptr(), v.data_ptr(), q.data_ptr(), m_in.data_ptr(),
                                               o.data_ptr(), m_out.data_ptr(), rows, T, K, V, decay, cabi.BF16,
@@ -173,14 +206,11 @@ def run_engine(args, rank, world, device):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    counter = {}
-
-    def timed_region_starts():
-        barrier()
-        counter["before"] = lib.grmx_launch_count()
-
-    total_ms, per_ms, window = time_launches(step, args.steps, args.warmup, timed_region_starts)
-    launches = lib.grmx_launch_count() - counter["before"]
+    # launches are counted where they are enqueued: the warm-up calls, then the captured steps
+    before_capture = lib.grmx_launch_count()
+    total_ms, per_ms, window = time_graph(step, args.steps, args.warmup, barrier)
+    launches = lib.grmx_launch_count() - before_capture
+    launches = launches * args.steps // (args.steps + args.warmup)       # the captured steps' share
     barrier()
     if world > 1:
         t = torch.tensor([total_ms], device=device, dtype=torch.float64)
@@ -239,6 +269,7 @@ def run_engine(args, rank, world, device):
             "tokens_per_step_per_gpu": tokens_per_step,
             "l2": f"inputs rotate over {n_sets} buffer sets ({n_sets * set_bytes / 1e6:.0f} MB > 126 MB L2)",
             "parallelism": f"batch x head rows sharded over {world} GPU(s), no collective",
+            "timing": "the timed steps are captured once into a CUDA graph; the timed region is one replay",
         },
         "row_token_units_per_s": world * rows * T * args.steps / (total_ms * 1e-3),
         "gpu_launches": int(launches),

@@ -50,28 +50,66 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // [B, T, D] bf16 tensor, box = 64 features x 128 tokens x 1 row, 128-byte swizzle
-bool make_token_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, int64_t D) {
+namespace {
+
+// Encoding a tensor map is a driver call of a few microseconds, and a scan needs four of them;
+// callers that run the same buffers again and again (a segment loop, a serving step) would pay
+// that on every call.  The last few encodings are kept per thread, keyed by everything that
+// goes into them.
+struct MapKey {
+  const void* base;
+  int64_t B, T, D;
+  int kind;   // 0: load map (64 x 128 box, 128-byte swizzle), 1: store map (32 x 128 box, 64-byte swizzle)
+  bool operator==(const MapKey& o) const {
+    return base == o.base && B == o.B && T == o.T && D == o.D && kind == o.kind;
+  }
+};
+constexpr int kMapCacheSlots = 16;
+struct MapCache {
+  MapKey keys[kMapCacheSlots];
+  CUtensorMap maps[kMapCacheSlots];
+  int used = 0;
+  int next = 0;
+};
+
+bool encode_token_map(CUtensorMap* map, const MapKey& key) {
+  thread_local MapCache cache;
+  for (int i = 0; i < cache.used; ++i) {
+    if (cache.keys[i] == key) {
+      *map = cache.maps[i];
+      return true;
+    }
+  }
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;
-  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(T) * D * 2};
-  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(key.D), static_cast<cuuint64_t>(key.T),
+                              static_cast<cuuint64_t>(key.B)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(key.D) * 2, static_cast<cuuint64_t>(key.T) * key.D * 2};
+  const cuuint32_t box[3] = {key.kind == 0 ? 64u : 32u, 128, 1};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
-                elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const bool ok =
+      encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(key.base), dims, strides, box, elem_strides,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, key.kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+             key.kind == 0 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (ok) {
+    const int slot = cache.next;
+    cache.keys[slot] = key;
+    cache.maps[slot] = *map;
+    cache.next = (slot + 1) % kMapCacheSlots;
+    if (cache.used < kMapCacheSlots) ++cache.used;
+  }
+  return ok;
+}
+
+}  // namespace
+
+bool make_token_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, int64_t D) {
+  return encode_token_map(map, MapKey{base, B, T, D, 0});
 }
 
 bool make_token_half_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, int64_t D) {
-  EncodeTiledFn encode = encode_tiled_fn();
-  if (encode == nullptr) return false;
-  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(T) * D * 2};
-  const cuuint32_t box[3] = {32, 128, 1};
-  const cuuint32_t elem_strides[3] = {1, 1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
-                elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
-                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_token_map(map, MapKey{base, B, T, D, 1});
 }
 
 bool device_is_sm100() {

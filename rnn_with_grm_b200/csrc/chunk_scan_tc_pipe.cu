@@ -333,15 +333,19 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         const int q_tokens = min(split.chunks_per_piece * kChunk, T - q * split.chunks_per_piece * kChunk);
         const float gq = powf(p.decay, static_cast<float>(q_tokens - first_offset(q * split.chunks_per_piece)));
         if (owns_row) {
-          const float4* part = reinterpret_cast<const float4*>(
-              split.partials + ((b * (split.pieces - 1) + q) * kD + state_row) * kD);
 #pragma unroll
-          for (int j = 0; j < kD / 4; ++j) {
-            const float4 x = __ldg(part + j);
-            m[4 * j] = fmaf(gq, m[4 * j], x.x);
-            m[4 * j + 1] = fmaf(gq, m[4 * j + 1], x.y);
-            m[4 * j + 2] = fmaf(gq, m[4 * j + 2], x.z);
-            m[4 * j + 3] = fmaf(gq, m[4 * j + 3], x.w);
+          for (int j = 0; j < kD; ++j) m[j] *= gq;
+          for (int sub = 0; sub < split.subs; ++sub) {
+            const float4* part = reinterpret_cast<const float4*>(
+                split.partials + (((b * (split.pieces - 1) + q) * split.subs + sub) * kD + state_row) * kD);
+#pragma unroll
+            for (int j = 0; j < kD / 4; ++j) {
+              const float4 x = __ldg(part + j);
+              m[4 * j] += x.x;
+              m[4 * j + 1] += x.y;
+              m[4 * j + 2] += x.z;
+              m[4 * j + 3] += x.w;
+            }
           }
         }
       }

@@ -5,7 +5,8 @@
 //   M_start(q+1) = decay^(tokens of piece q) * M_start(q) + L_q,
 //   L_q = sum over the tokens j of piece q of coeff * decay^(n_q - 1 - step_j) v_j k_j^T,
 // and L_q depends on k and v of piece q only.  `piece_state_kernel` below computes the
-// L_q of every piece but the last (one CTA per piece and row: TMA-fed tcgen05.mma
+// L_q of every piece but the last, each as the sum of `subs` terms over consecutive runs of
+// chunks so that this kernel fills the GPU too (one CTA per term: TMA-fed tcgen05.mma
 // accumulating Vw^T Kc in TMEM, no rescaling between chunks because the decay of the whole
 // piece is folded into the per-token weights) into a scratch buffer the caller provides; the
 // scan kernel launched after it on the same stream rebuilds each piece's start state from
@@ -64,12 +65,16 @@ piece_state_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int64_t b = blockIdx.x % p.B;
-  const int piece = static_cast<int>(blockIdx.x / p.B);
+  const int piece = static_cast<int>(blockIdx.x / p.B) / split.subs;
+  const int sub = static_cast<int>(blockIdx.x / p.B) % split.subs;
   const int T = static_cast<int>(p.T);
   const bool rev = p.reverse != 0;
-  const int c_begin = piece * split.chunks_per_piece;
-  const int n_chunks = split.chunks_per_piece;                       // pieces before the last are full
-  const int piece_tokens = min(n_chunks * kChunk, T - c_begin * kChunk);
+  // pieces before the last are full; this CTA covers chunks [sub_begin, sub_begin + n_chunks) of its piece
+  const int per_sub = (split.chunks_per_piece + split.subs - 1) / split.subs;
+  const int sub_begin = sub * per_sub;
+  const int n_chunks = max(0, min(per_sub, split.chunks_per_piece - sub_begin));
+  const int c_begin = piece * split.chunks_per_piece + sub_begin;
+  const int piece_tokens = min(split.chunks_per_piece * kChunk, T - piece * split.chunks_per_piece * kChunk);
   auto chunk_len = [&](int c) { return min(kChunk, T - c * kChunk); };
   auto chunk_token0 = [&](int c) { return rev ? T - (c + 1) * kChunk : c * kChunk; };
 
@@ -154,18 +159,24 @@ piece_state_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       } while (false);
       if (!ok) break;
       // weight of this token: every later token of the piece decays it once more
-      const int later = piece_tokens - 1 - (c * kChunk + step);
+      const int later = piece_tokens - 1 - ((sub_begin + c) * kChunk + step);
       const float w = step < chunk_len(c_begin + c) ? p.update_coeff * powf(p.decay, static_cast<float>(later)) : 0.0f;
       scaled_row_copy(stage_v(c % kStages), vw_buf(c & 1), row, w);
       fence_proxy_async();
       mbar_arrive(&bar_vw_ready[c & 1]);
     }
     const int last = n_chunks - 1;
-    if (ok && mbar_wait(&bar_d_done[last & 1], (last / 2) & 1, s_abort)) {
+    float* out = partials +
+                 (((b * (split.pieces - 1) + piece) * split.subs + sub) * kD + (warp * 16 + (lane & 15))) * kD;
+    if (n_chunks == 0) {
+      // a term without chunks (uneven division) contributes nothing
+      if (lane < 16) {
+        for (int j = 0; j < kD; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    } else if (ok && mbar_wait(&bar_d_done[last & 1], (last / 2) & 1, s_abort)) {
       tc_fence_after();
       // M = 64 accumulator: lanes 0-15 of each 32-lane quarter hold rows 16*warp + lane
       const uint32_t tmem_lane = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-      float* out = partials + ((b * (split.pieces - 1) + piece) * kD + (warp * 16 + (lane & 15))) * kD;
 #pragma unroll 1
       for (int c0 = 0; c0 < kD; c0 += 32) {
         float v[32];
@@ -209,27 +220,44 @@ int pick_pieces(const ScanParams& p) {
   return pieces;
 }
 
+// Terms per piece state: the largest power of two that keeps the piece-state kernel within one
+// wave and gives every term two chunks or more.
+int pick_subs(const ScanParams& p, int pieces, int chunks_per_piece) {
+  const int sms = sm_count_of_current_device();
+  int subs = 1;
+  while (p.B * (pieces - 1) * subs * 2 <= sms && chunks_per_piece / (subs * 2) >= 2) subs *= 2;
+  return subs;
+}
+
+// the cut for this call: pieces == 1 when a cut does not apply
+SplitInfo plan_split(const ScanParams& p) {
+  const int64_t n_chunks = (p.T + kChunk - 1) / kChunk;
+  SplitInfo split{1, static_cast<int>(n_chunks), nullptr, 1};
+  const int pieces = pick_pieces(p);
+  if (pieces <= 1) return split;
+  const int per_piece = static_cast<int>((n_chunks + pieces - 1) / pieces);
+  if (static_cast<int64_t>(per_piece) * (pieces - 1) >= n_chunks) return split;   // every piece must own a chunk
+  split.pieces = pieces;
+  split.chunks_per_piece = per_piece;
+  split.subs = pick_subs(p, pieces, per_piece);
+  return split;
+}
+
 }  // namespace
 
 int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p) {
-  const int pieces = pick_pieces(p);
-  if (pieces <= 1) return 0;
-  return p.B * (pieces - 1) * kD * kD * static_cast<int64_t>(sizeof(float));
+  const SplitInfo split = plan_split(p);
+  if (split.pieces <= 1) return 0;
+  return p.B * (split.pieces - 1) * split.subs * kD * kD * static_cast<int64_t>(sizeof(float));
 }
 
 int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
   const int64_t n_chunks = (p.T + kChunk - 1) / kChunk;
-  const int pieces = pick_pieces(p);
-  const int64_t need = p.B * (pieces - 1) * kD * kD * static_cast<int64_t>(sizeof(float));
+  SplitInfo split = plan_split(p);
+  const int pieces = split.pieces;
+  const int64_t need = p.B * (pieces - 1) * split.subs * kD * kD * static_cast<int64_t>(sizeof(float));
   if (pieces <= 1 || scratch == nullptr || scratch_bytes < need ||
       (reinterpret_cast<uintptr_t>(scratch) & 15u) != 0) {
-    return launch_scan_tcgen05_pipe(p, SplitInfo{1, static_cast<int>(n_chunks), nullptr}, stream);
-  }
-  SplitInfo split;
-  split.pieces = pieces;
-  split.chunks_per_piece = static_cast<int>((n_chunks + pieces - 1) / pieces);
-  // every piece must own at least one chunk
-  if (static_cast<int64_t>(split.chunks_per_piece) * (pieces - 1) >= n_chunks) {
     return launch_scan_tcgen05_pipe(p, SplitInfo{1, static_cast<int>(n_chunks), nullptr}, stream);
   }
   split.partials = static_cast<const float*>(scratch);
@@ -254,7 +282,7 @@ int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratc
   if (!make_token_map(&map_k, p.keys, p.B, p.T, kD) || !make_token_map(&map_v, p.values, p.B, p.T, kD)) {
     return fail(GRMX_ERR_LAUNCH, "piece-state kernel: cuTensorMapEncodeTiled failed");
   }
-  piece_state_kernel<<<static_cast<unsigned>(p.B * (pieces - 1)), kThreads, kSmemAlloc, stream>>>(
+  piece_state_kernel<<<static_cast<unsigned>(p.B * (pieces - 1) * split.subs), kThreads, kSmemAlloc, stream>>>(
       map_k, map_v, p, split, static_cast<float*>(scratch), device_error_word_ptr());
   int rc = check_launch("piece_state_kernel");
   if (rc != GRMX_OK) return rc;

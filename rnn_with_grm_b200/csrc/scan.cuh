@@ -34,7 +34,9 @@ int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream);
 struct SplitInfo {
   int pieces;              // CTAs per batch row
   int chunks_per_piece;    // 128-token chunks handled by each of them
-  const float* partials;   // [B, pieces-1, H, K] fp32: local state contribution of pieces 0..pieces-2
+  const float* partials;   // [B, pieces-1, subs, H, K] fp32: local state contribution of pieces
+                           // 0..pieces-2, each as the sum of `subs` terms (computed by separate CTAs)
+  int subs = 1;
 };
 
 // Warp-specialised variant of the tcgen05 scan (d_k = d_v = 64); same coverage rules otherwise.

@@ -438,7 +438,8 @@ def test_tcgen05_scan_cut_along_time_matches_uncut(B, T):
 
 
 def test_scratch_size_query():
-    assert gx.chunk_scan_scratch_bytes(64, 2048, 64, 64, torch.bfloat16, torch.float32) == 64 * 64 * 64 * 4
+    # 64 rows on 148 SMs: two pieces, the first piece's state as the sum of two terms
+    assert gx.chunk_scan_scratch_bytes(64, 2048, 64, 64, torch.bfloat16, torch.float32) == 64 * 2 * 64 * 64 * 4
     assert gx.chunk_scan_scratch_bytes(512, 2048, 64, 64, torch.bfloat16, torch.float32) == 0    # enough rows
     assert gx.chunk_scan_scratch_bytes(64, 256, 64, 64, torch.bfloat16, torch.float32) == 0      # too short
     assert gx.chunk_scan_scratch_bytes(64, 2048, 64, 64, torch.float32, torch.float32) == 0      # fp32 path
