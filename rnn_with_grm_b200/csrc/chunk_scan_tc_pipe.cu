@@ -14,18 +14,18 @@
 // tensor-core product of the chunk before it except through the state, and the state costs one
 // register FMA and one shared-memory store per chunk: the rest is a pipeline.  Roles:
 //
-//   warp 12      issuer A: [S | R]_c; owns the TMEM allocation
-//   warp 13      issuer B: U_c, up to two chunks ahead
-//   warp 14      issuer C: A_c
-//   warp 15      loader: TMA ring of three stages, refilled as soon as a chunk's tiles are dead
+//   warp 20      issuer A: [S | R]_c; owns the TMEM allocation
+//   warp 21      issuer B: U_c, up to two chunks ahead
+//   warp 22      issuer C: A_c
+//   warp 23      loader: TMA ring of three stages, refilled as soon as a chunk's tiles are dead
 //                (issuers run as whole warps with one elected lane executing the instruction)
-//   warps 8-11   state group: Vw_c, the decay-scaled copy of V; the state, one row per thread in
+//   warps 16-19  state group: Vw_c, the decay-scaled copy of V; the state, one row per thread in
 //                lanes 0-15 of each warp (the layout of a 64-row accumulator),
 //                M_c = decay^len M_{c-1} + U_c, and its bf16 copy behind the K tile of chunk c+1
-//   warps 0-3    compute group 0: columns 0-63 of S_c, output columns 0-31
-//   warps 4-7    compute group 1: columns 64-127 of S_c, output columns 32-63
-//                each: S_c -> P_c (decay mask, bf16, written back into the TMEM columns of S_c),
-//                      then the epilogue of chunk c-1 (R, A -> out -> HBM)
+//   warps 0-7    P groups 0 and 1: S_c -> P_c (decay mask, bf16, written back into the TMEM
+//                columns of S_c), two 32-column blocks per group
+//   warps 8-15   epilogue groups 2 and 3: R_c, A_c -> out -> shared memory -> TMA store, 32 output
+//                columns per group; runs beside the P pass of the next chunk
 //
 // P never touches shared memory: A = P Vc takes its left operand from TMEM.  Shared memory holds
 // three stages [q | k | Mb | v] (the state copy sits right behind k so that [Kc ; Mb] is one
@@ -49,13 +49,24 @@ using namespace tc;
 constexpr int kChunk = 128;
 constexpr int kD = 64;                 // d_k == d_v
 constexpr int kStages = 3;
-constexpr int kThreads = 512;          // 16 warps, 128 registers per thread
-constexpr int kStateWarp0 = 8;         // warps 8-11
+constexpr int kThreads = 768;          // 24 warps; registers are re-divided between the roles at entry
+constexpr int kComputeGroups = 4;      // warps 0-15, four per group
+constexpr int kComputeThreads = kComputeGroups * 128;
+constexpr int kStateWarp0 = 16;        // warps 16-19
 constexpr int kStateThreads = 128;
-constexpr int kIssuerA = 12;           // [S | R]; also owns the TMEM allocation
-constexpr int kIssuerB = 13;           // U
-constexpr int kIssuerC = 14;           // A = P V
-constexpr int kLoader = 15;            // TMA
+constexpr int kIssuerA = 20;           // [S | R]; also owns the TMEM allocation
+constexpr int kIssuerB = 21;           // U
+constexpr int kIssuerC = 22;           // A = P V
+constexpr int kLoader = 23;            // TMA
+// registers per thread after the re-division (768 threads start with 80 each)
+constexpr int kRegsCompute = 72;
+constexpr int kRegsState = 128;
+constexpr int kRegsIssue = 40;
+// setmaxnreg.inc can only take what the other warps of the CTA have released with setmaxnreg.dec (it
+// blocks until then), so the books have to balance within the launch allocation
+constexpr int kRegsLaunch = 80;        // 65536 / 768, rounded down to a multiple of 8
+static_assert(kComputeThreads * kRegsCompute + kStateThreads * kRegsState + 128 * kRegsIssue <= kThreads * kRegsLaunch,
+              "the state group would wait for registers that nobody releases");
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColBuf = 0;        // + 192 * (c & 1): S (0-127) -> P (0-63, bf16 pairs), A (64-127), R (128-191)
 constexpr uint32_t kBufCols = 192;
@@ -83,7 +94,7 @@ constexpr int kOffOut = kOffVw + 2 * kTileBytes;
 constexpr int kOffWtab = kOffOut + 2 * kOutBytes;
 constexpr int kOffPow = kOffWtab + 4 * kWcopy * 4;   // float[kChunk + 4]: decay^j
 constexpr int kOffBars = kOffPow + (kChunk + 4) * 4;
-constexpr int kNumBars = 32;
+constexpr int kNumBars = 36;
 constexpr int kOffMisc = kOffBars + kNumBars * 8;
 constexpr int kSmemTotal = kOffMisc + 32;
 constexpr int kSmemAlloc = kSmemTotal + 1024;
@@ -117,9 +128,9 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   uint64_t* bar_mb_ready = bars + 16;     // [3] bf16 copy of the state before chunk c        (128)
   uint64_t* bar_u_free = bars + 20;       // [2] U_c folded into the state                    (128)
   uint64_t* bar_stage_free = bars + 22;   // [3] U_c and A_c complete: the tiles of chunk c are dead (2)
-  uint64_t* bar_s_read = bars + 26;       // [2] compute group 0 has S block 1 in registers   (128)
-  uint64_t* bar_out_ready = bars + 28;    // [2] group g has written its half of the output tile (128)
-  uint64_t* bar_out_free = bars + 30;     // [2] the store of that half tile has read it      (1)
+  uint64_t* bar_s_read = bars + 26;       // [2] P group 0 has S block 1 in registers         (128)
+  uint64_t* bar_out_ready = bars + 30;    // [2] epilogue group h has written its half of the output tile (128)
+  uint64_t* bar_out_free = bars + 32;     // [2] the store of that half tile has read it      (1)
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kOffMisc);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kOffMisc + 8);
 
@@ -197,7 +208,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   // never more than one completion behind, because the producer's next completion on the same
   // barrier needs something that comes after the waiter's wait:
   //   loader:   TMA of c    needs stage_free(c-3): one arrival after u_done(c-3) (state group), one
-  //                         after a_done(c-3) (epilogue), which also follows [S | R]_{c-3}
+  //                         after a_done(c-3) (issuer C), which also follows [S | R]_{c-3}
   //   issuer A: [S | R]_c   needs full(c), mb_ready(c), buf_free(c-2)
   //   state:    Vw_c        needs full(c) and u_done(c-2) (waited for M_{c-2}, earlier in program order)
   //             M_c         needs u_done(c); its bf16 copy goes behind the K tile of chunk c+1, whose
@@ -210,6 +221,11 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   // A issues after passing mb_ready(c); with two barriers the loads of the prologue would leave a
   // window.
 
+  // The register file is re-divided at the top of each role (setmaxnreg works on groups of four
+  // warps): the state group keeps a 64-register state row per thread, the compute groups need
+  // little more than one 32-column block, the issuers next to nothing.
+  if (warp >= kIssuerA) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsIssue));
   if (warp == kIssuerA) {
     // ===================================================================== issuer A: [S | R]
     const uint32_t leader = elect_one();
@@ -281,9 +297,15 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         tc_mma_bf16_ts_if(leader, buf + kColA, buf + 8u * kk, desc_add(dv_mn, kk * 2048), idesc_a, kk > 0);
       }
       tc_commit_if(leader, &bar_a_done[c & 1]);
+      // The next P pass is a whole chunk period away, so this warp has the time to see A_c finish
+      // and to hand the stage back to the loader at once.
+      GRMX_WAIT(&bar_a_done[c & 1], c / 2)
+      if (leader) mbar_arrive(&bar_stage_free[c % kStages]);
     }
+  }
   } else if (warp >= kStateWarp0) {
-    // ===================================================================== state group (warps 8-11)
+    // ===================================================================== state group (warps 16-19)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsState));
     const int row = tid - kStateWarp0 * 32;   // token row of the copy
     const int step = rev ? kChunk - 1 - row : row;
     const int quarter = warp - kStateWarp0;
@@ -403,134 +425,132 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       }
     } while (false);
   } else {
-    // ===================================================================== compute groups (warps 0-7)
-    // Both groups work on every chunk and split it by columns: group g turns the 32-column blocks
-    // 2g and 2g+1 of S into P, and writes the output columns 32g .. 32g+31.  Warp w of a group owns
-    // rows 32w .. 32w+31, so blocks above block w (below it in a reverse scan) are all zero.
-    // P block blk (16 packed columns) lands on S columns 16*blk .. 16*blk+15: group 0 overwrites
-    // what it has read itself, group 1 overwrites S block 1, which group 0 reads, and waits for
-    // s_read(c) before it stores.
+    // ===================================================================== compute groups (warps 0-15)
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsCompute));
+    // Groups 0 and 1 turn S into P, groups 2 and 3 write the output: the P pass of chunk c+1 and
+    // the epilogue of chunk c run side by side.  Warp w of a group owns rows 32w .. 32w+31.
     const int g = warp >> 2;
     const int quarter = warp & 3;
     const int row = tid & 127;                // token row within the chunk == TMEM lane
     const int step = rev ? kChunk - 1 - row : row;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kColBuf;
-    const bool nz0 = rev ? 2 * g >= quarter : 2 * g <= quarter;            // block 2g is not all zero
-    const bool nz1 = rev ? 2 * g + 1 >= quarter : 2 * g + 1 <= quarter;    // block 2g+1
-    const int m_first = 127 - row + 64 * g;   // reversed-table index of column 64g
 
-    for (int c = 0; c <= n_chunks; ++c) {
-      if (c < n_chunks) {
-        // ---- P pass: S_c -> P_c in place ----
+    if (g < 2) {
+      // ---- P groups: group g turns the 32-column blocks 2g and 2g+1 of S into P ----
+      // Blocks above block w (below it in a reverse scan) are all zero.  P block blk (16 packed
+      // columns) lands on S columns 16*blk .. 16*blk+15: group 0 overwrites S block 0 after
+      // reading it; group 1 overwrites S block 1, which group 0 reads second, and waits for
+      // s_read(c) before it stores.
+      for (int c = 0; c < n_chunks; ++c) {
         const uint32_t buf_row = lane_base + kBufCols * (c & 1);
         GRMX_WAIT(&bar_s_done[c & 1], c / 2)
         tc_fence_after();
-        uint32_t sv0[32], sv1[32], pk[16];
-        if (nz0) tc_ld32_async(buf_row + 64u * g, sv0);
-        if (nz1) tc_ld32_async(buf_row + 64u * g + 32u, sv1);
-        tc_wait_ld();
-        if (g == 0) {
-          tc_fence_before();
-          mbar_arrive(&bar_s_read[c & 1]);
-        }
-        if (nz0) {
-          const int m0 = m_first;
-          const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
 #pragma unroll
-          for (int t = 0; t < 8; ++t) {
-            const float4 w4 = wv[t];
-            pk[2 * t] = pack_bf16(__uint_as_float(sv0[4 * t]) * w4.x, __uint_as_float(sv0[4 * t + 1]) * w4.y);
-            pk[2 * t + 1] = pack_bf16(__uint_as_float(sv0[4 * t + 2]) * w4.z, __uint_as_float(sv0[4 * t + 3]) * w4.w);
+        for (int k = 0; k < 2; ++k) {
+          const int blk = 2 * g + k;
+          const bool nz = rev ? blk >= quarter : blk <= quarter;
+          uint32_t sv[32], pk[16];
+          if (nz) {
+            tc_ld32_async(buf_row + 32u * blk, sv);
+            tc_wait_ld();
           }
-        } else {
-#pragma unroll
-          for (int t = 0; t < 16; ++t) pk[t] = 0u;
-        }
-        if (g == 1) {
-          GRMX_WAIT(&bar_s_read[c & 1], c / 2)
-        }
-        tc_st16_async(buf_row + 32u * g, pk);
-        if (nz1) {
-          const int m0 = m_first + 32;
-          const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
-#pragma unroll
-          for (int t = 0; t < 8; ++t) {
-            const float4 w4 = wv[t];
-            pk[2 * t] = pack_bf16(__uint_as_float(sv1[4 * t]) * w4.x, __uint_as_float(sv1[4 * t + 1]) * w4.y);
-            pk[2 * t + 1] = pack_bf16(__uint_as_float(sv1[4 * t + 2]) * w4.z, __uint_as_float(sv1[4 * t + 3]) * w4.w);
+          if (g == 0 && k == 1) {
+            tc_fence_before();
+            mbar_arrive(&bar_s_read[c & 1]);
           }
-        } else {
+          if (nz) {
+            const int m0 = 127 - row + 32 * blk;            // reversed-table index of column 32*blk
+            const float4* wv = reinterpret_cast<const float4*>(s_wtab + (m0 & 3) * kWcopy + (m0 & ~3));
 #pragma unroll
-          for (int t = 0; t < 16; ++t) pk[t] = 0u;
+            for (int t = 0; t < 8; ++t) {
+              const float4 w4 = wv[t];
+              pk[2 * t] = pack_bf16(__uint_as_float(sv[4 * t]) * w4.x, __uint_as_float(sv[4 * t + 1]) * w4.y);
+              pk[2 * t + 1] = pack_bf16(__uint_as_float(sv[4 * t + 2]) * w4.z, __uint_as_float(sv[4 * t + 3]) * w4.w);
+            }
+          } else {
+#pragma unroll
+            for (int t = 0; t < 16; ++t) pk[t] = 0u;
+          }
+          if (g == 1 && k == 0) {
+            GRMX_WAIT(&bar_s_read[c & 1], c / 2)
+          }
+          tc_st16_async(buf_row + 16u * blk, pk);
         }
-        tc_st16_async(buf_row + 32u * g + 16u, pk);
+        if (*s_abort) break;
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&bar_p_ready[c & 1]);
       }
-      if (c >= 1) {
-        // ---- epilogue of chunk c-1: out_i = hs * decay^(i+1) R_i + A_i -> bf16 -> HBM ----
-        const int e = c - 1;
+    } else {
+      // ---- epilogue groups: group 2+h writes the output columns 32h .. 32h+31 ----
+      // out_i = hs * decay^(i+1) R_i + A_i -> bf16 -> HBM.  The half tile goes out as one TMA store
+      // from shared memory (plain 16-byte stores at a 128-byte stride cost the load/store unit one
+      // line per lane).  A store may not start at a negative token, which the short last chunk of
+      // a reverse scan does: that one is written with plain stores.  The hand-offs run for every
+      // chunk so that phases stay e.
+      const int h = g - 2;
+      uint8_t* s_out = smem + kOffOut + h * kOutBytes;
+      for (int e = 0; e < n_chunks; ++e) {
         const uint32_t buf_row = lane_base + kBufCols * (e & 1);
         GRMX_WAIT(&bar_a_done[e & 1], e / 2)
-        if (tid == 0) mbar_arrive(&bar_stage_free[e % kStages]);
         tc_fence_after();
         const int ge = c_begin + e;
         const bool row_live = step < chunk_len(ge);
         const float r_scale = row_live ? p.hidden_scale * s_pow[step + 1 - first_offset(ge)] : 0.0f;
-        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.hidden_out) +
-                             (b * p.T + static_cast<int64_t>(chunk_token0(ge)) + row) * kD + 32 * g;
-        uint32_t av[32], rv[32];
-        tc_ld32_async(buf_row + kColA + 32u * g, av);
-        tc_ld32_async(buf_row + kColR + 32u * g, rv);
-        tc_wait_ld();
-        tc_fence_before();
-        mbar_arrive(&bar_buf_free[e & 1]);   // the values are in registers: the buffer may be reused
-        // The half tile goes out as one TMA store from shared memory (plain 16-byte stores at a
-        // 128-byte stride cost the load/store unit one line per lane).  A store may not start at a
-        // negative token, which the short last chunk of a reverse scan does: that one is written
-        // with plain stores.  The hand-offs below run for every chunk so that phases stay e.
         const int t0 = chunk_token0(ge);
         const bool by_tma = t0 >= 0;
-        uint8_t* s_out = smem + kOffOut + g * kOutBytes;
         if (e >= 1) {
           if (row == 0) {
             bulk_wait_read();
-            mbar_arrive(&bar_out_free[g]);
+            mbar_arrive(&bar_out_free[h]);
           }
-          GRMX_WAIT(&bar_out_free[g], e - 1)
+          GRMX_WAIT(&bar_out_free[h], e - 1)
         }
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          float o[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            o[i] = fmaf(r_scale, __uint_as_float(rv[ch * 8 + i]), __uint_as_float(av[ch * 8 + i]));
+        for (int half = 0; half < 2; ++half) {
+          uint32_t av[16], rv[16];
+          tc_ld16_async(buf_row + kColA + 32u * h + 16u * half, av);
+          tc_ld16_async(buf_row + kColR + 32u * h + 16u * half, rv);
+          tc_wait_ld();
+          if (half == 1) {
+            tc_fence_before();
+            mbar_arrive(&bar_buf_free[e & 1]);   // the values are in registers: the buffer may be reused
           }
-          uint4 w;
-          w.x = pack_bf16(o[0], o[1]);
-          w.y = pack_bf16(o[2], o[3]);
-          w.z = pack_bf16(o[4], o[5]);
-          w.w = pack_bf16(o[6], o[7]);
-          if (by_tma) {
-            // 64-byte rows, 64-byte swizzle: 16-byte piece j of row r sits at position j ^ ((r >> 1) & 3)
-            *reinterpret_cast<uint4*>(s_out + row * 64 + ((ch ^ ((row >> 1) & 3)) * 16)) = w;
-          } else if (row_live) {
-            *reinterpret_cast<uint4*>(out + ch * 8) = w;
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              o[i] = fmaf(r_scale, __uint_as_float(rv[ch * 8 + i]), __uint_as_float(av[ch * 8 + i]));
+            }
+            uint4 w;
+            w.x = pack_bf16(o[0], o[1]);
+            w.y = pack_bf16(o[2], o[3]);
+            w.z = pack_bf16(o[4], o[5]);
+            w.w = pack_bf16(o[6], o[7]);
+            const int piece16 = 2 * half + ch;              // 16-byte piece of the 64-byte half row
+            if (by_tma) {
+              // 64-byte rows, 64-byte swizzle: piece j of row r sits at position j ^ ((r >> 1) & 3)
+              *reinterpret_cast<uint4*>(s_out + row * 64 + ((piece16 ^ ((row >> 1) & 3)) * 16)) = w;
+            } else if (row_live) {
+              __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.hidden_out) +
+                                   (b * p.T + static_cast<int64_t>(t0) + row) * kD + 32 * h;
+              *reinterpret_cast<uint4*>(out + piece16 * 8) = w;
+            }
           }
         }
         fence_proxy_async();
-        mbar_arrive(&bar_out_ready[g]);
+        mbar_arrive(&bar_out_ready[h]);
         if (row == 0) {
-          GRMX_WAIT(&bar_out_ready[g], e)
+          GRMX_WAIT(&bar_out_ready[h], e)
           if (by_tma) {
-            tma_store_3d(s_out, &map_o, 32 * g, t0, static_cast<int>(b));
+            tma_store_3d(s_out, &map_o, 32 * h, t0, static_cast<int>(b));
             bulk_commit();
           }
         }
       }
+      if (row == 0) bulk_wait_read();   // the last store still reads shared memory
     }
-    if (row == 0) bulk_wait_read();   // the last store still reads shared memory
   }
 #undef GRMX_WAIT
 
