@@ -392,11 +392,12 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         {
           const float carry = s_pow[chunk_len(c_begin + c) - first_offset(c_begin + c)];
 #pragma unroll
-          for (int part = 0; part < 4; ++part) {
-            float u[16];
-            tc_ld16(tmem_lane + kColU + 64u * (c & 1) + 16u * part, u);
+          for (int half = 0; half < 2; ++half) {
+            uint32_t u[32];
+            tc_ld32_async(tmem_lane + kColU + 64u * (c & 1) + 32u * half, u);
+            tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) m[16 * part + j] = fmaf(carry, m[16 * part + j], u[j]);
+            for (int j = 0; j < 32; ++j) m[32 * half + j] = fmaf(carry, m[32 * half + j], __uint_as_float(u[j]));
           }
         }
         tc_fence_before();
