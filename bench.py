@@ -281,7 +281,9 @@ def run_engine(args, rank, world, device):
             "unit": "GB/s",
             "frac": achieved_gbs / hbm_peak,
             "peak_source": peak_kind,
-            "traffic": None,
+            # DRAM bytes of one step from the ncu capture of this workload (profiles/): scan kernel
+            # 53.6 MB read + 2.4 MB written, piece-state kernel 16.8 MB read
+            "traffic": 72783616 if kernels_per_step > 1.5 else None,
             "algorithmic_bytes_per_launch": algo_bytes,
             "launch_ms": launch_ms,
             "tensor_tflops": algo_flops / (launch_ms * 1e-3) / 1e12,
@@ -304,11 +306,37 @@ def run_engine(args, rank, world, device):
     return result
 
 
+def full_occupancy_scan(lib, device, hbm_peak, launches=5):
+    """The scan kernel with one batch row per SM and a long sequence: the shape at which the kernel,
+    not the number of rows, sets the time.  Timed as one CUDA graph of `launches` launches over
+    inputs (0.6 GB) larger than L2."""
+    from rnn_with_grm_b200 import cabi
+
+    rows = torch.cuda.get_device_properties(device).multi_processor_count
+    T, K, V, decay = 8192, CFG2["K"], CFG2["V"], CFG2["decay"]
+    k, v, q = make_scan_inputs(rows, T, K, V, device, seed=7)
+    o = torch.empty_like(v)
+    m_in = torch.zeros(rows, V, K, device=device)
+    m_out = torch.empty_like(m_in)
+
+    def scan(_, stream):
+        cabi.check(lib.grmx_chunk_scan_fwd(k.data_ptr(), v.data_ptr(), q.data_ptr(), m_in.data_ptr(), o.data_ptr(),
+                                           m_out.data_ptr(), rows, T, K, V, decay, cabi.BF16, cabi.F32,
+                                           cabi.PATH_AUTO, stream))
+
+    total_ms, _, _ = time_graph(scan, launches, 3)
+    ms = total_ms / launches
+    nbytes = rows * T * (2 * (2 * K + V) + 2 * V)
+    return {"rows": rows, "T": T, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_peak,
+            "bytes": nbytes, "row_tokens_per_s": rows * T / (ms * 1e-3)}
+
+
 def other_workloads(lib, device, hbm_peak):
     """Kernel-timed figures for the retrieval path (config 3) and a config-5 slab."""
     from rnn_with_grm_b200 import cabi
 
     out = {}
+    out["full_occupancy_scan"] = full_occupancy_scan(lib, device, hbm_peak)
     stream = torch.cuda.current_stream().cuda_stream
     # ---- config 3: one query per segment, causal top-4 over 32 archived 64x64 fp32 matrices ----
     rows, S, K, V, top_k = CFG3["B"] * CFG3["Hd"], CFG3["T"] // CFG3["segment"], CFG3["K"], CFG3["V"], CFG3["top_k"]
@@ -464,6 +492,8 @@ def main(argv=None) -> int:
     parser.add_argument("--impl", choices=["engine", "reference"], default="engine")
     parser.add_argument("--skip-extras", action="store_true",
                         help="main workload only: no CPU baseline, no other workloads (small footprint for profiling)")
+    parser.add_argument("--full-occupancy-only", action="store_true",
+                        help="run only the one-row-per-SM scan of the extras and print its figures (for profiling)")
     args = parser.parse_args(argv)
     args.warmup = max(args.warmup, 3)
 
@@ -486,6 +516,10 @@ def main(argv=None) -> int:
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=device)
+    if args.full_occupancy_only:
+        from rnn_with_grm_b200 import cabi
+        print(json.dumps({"full_occupancy_scan": full_occupancy_scan(cabi.load(), device, load_peaks()[0])}), flush=True)
+        return 0
     try:
         result = run_engine(args, rank, world, device)
         if result is not None:
