@@ -15,6 +15,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxRoutes = 32;
+constexpr int kRows = 2;               // matrix rows per lane group with loads in flight together
 
 template <int VEC>
 __device__ __forceinline__ void load_row_chunk(const float* p, float (&out)[VEC]) {
@@ -41,13 +42,16 @@ __device__ __forceinline__ float block_sum(float v, float* s_red) {
   return total;
 }
 
-template <int VEC>
+// VEC floats per load, G lanes per matrix row (G * VEC divides into K in whole steps or covers it
+// once), kPerRoute: the per-route products are the result (mode "retrieved"); otherwise the gate
+// weights are applied lane by lane before the one reduction per row.
+template <int VEC, int G, bool kPerRoute>
 __global__ void __launch_bounds__(kThreads)
 retrieve_fuse_kernel(const float* __restrict__ archive, const int64_t* __restrict__ indices,
                      const float* __restrict__ gates, const float* __restrict__ queries,
                      const float* __restrict__ online, const float* __restrict__ ln_weight,
                      const float* __restrict__ ln_bias, float ln_eps, float* __restrict__ out,
-                     int64_t S, int64_t Q, int R, int H, int K, int G, int mode,
+                     int64_t S, int64_t Q, int R, int H, int K, int mode,
                      uint32_t* __restrict__ error_word) {
   extern __shared__ float s_mem[];
   float* s_q = s_mem;             // [K]
@@ -78,57 +82,91 @@ retrieve_fuse_kernel(const float* __restrict__ archive, const int64_t* __restric
   const float* arch_b = archive + b * S * (int64_t)H * K;
   const int lane_in_group = threadIdx.x % G;
   const int group = threadIdx.x / G;
-  const int groups = kThreads / G;
+  constexpr int groups = kThreads / G;
   const int iters = (H + groups - 1) / groups;
 
-  for (int it = 0; it < iters; ++it) {
-    const int h = it * groups + group;
-    float contrib = 0.0f;
-    // four routes at a time so that their loads are all issued before use
+  // kRows matrix rows per group at a time, four routes each: all of their loads (kRows x 4 x 16 bytes
+  // per lane) are issued before the first use.  The kernel is bound by instruction issue, not by
+  // bytes in flight, so the loops below are fully unrolled over compile-time lane counts, and for the
+  // fused modes the gate-weighted sum over routes is formed per lane (in route order) before the
+  // single reduction of a row over its G lanes.
+  for (int it0 = 0; it0 < iters; it0 += kRows) {
+    float contrib[kRows];
+#pragma unroll
+    for (int v = 0; v < kRows; ++v) contrib[v] = 0.0f;
     for (int r0 = 0; r0 < R; r0 += 4) {
-      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      const float* row[4];
+      float acc[kRows][4];
+      const float* row[kRows][4];
+      float gate[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int64_t seg = r0 + u < R ? s_idx[r0 + u] : -1;
-        row[u] = (seg >= 0 && h < H) ? arch_b + (seg * H + h) * (int64_t)K : nullptr;
+        gate[u] = seg >= 0 ? s_gate[r0 + u] : 0.0f;
+        const float* mat = seg >= 0 ? arch_b + seg * H * (int64_t)K : nullptr;
+#pragma unroll
+        for (int v = 0; v < kRows; ++v) {
+          const int h = (it0 + v) * groups + group;
+          row[v][u] = (mat != nullptr && h < H) ? mat + h * (int64_t)K : nullptr;
+          acc[v][u] = 0.0f;
+        }
       }
       for (int k0 = lane_in_group * VEC; k0 < K; k0 += G * VEC) {
-        float m[4][VEC];
+        float m[kRows][4][VEC];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (row[u] != nullptr) {
-            load_row_chunk<VEC>(row[u] + k0, m[u]);
-          } else {
+        for (int v = 0; v < kRows; ++v) {
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) m[u][j] = 0.0f;
+          for (int u = 0; u < 4; ++u) {
+            if (row[v][u] != nullptr) {
+              load_row_chunk<VEC>(row[v][u] + k0, m[v][u]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < VEC; ++j) m[v][u][j] = 0.0f;
+            }
           }
         }
+        float qv[VEC];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int j = 0; j < VEC; ++j) qv[j] = s_q[k0 + j];
 #pragma unroll
-          for (int j = 0; j < VEC; ++j) acc[u] = fmaf(m[u][j], s_q[k0 + j], acc[u]);
+        for (int v = 0; v < kRows; ++v) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[v][u] = fmaf(m[v][u][j], qv[j], acc[v][u]);
+          }
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        float a = acc[u];
-        for (int o = G >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        const int r = r0 + u;
-        if (r < R) {
-          if (mode == GRMX_FUSE_RETRIEVED) {
-            if (lane_in_group == 0 && h < H) out[(bq * R + r) * (int64_t)H + h] = a;
-          } else if (s_idx[r] >= 0) {
-            contrib = fmaf(s_gate[r], a, contrib);
+      for (int v = 0; v < kRows; ++v) {
+        if constexpr (kPerRoute) {
+          const int h = (it0 + v) * groups + group;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float a = acc[v][u];
+#pragma unroll
+            for (int o = G >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+            if (r0 + u < R && lane_in_group == 0 && h < H) out[(bq * R + r0 + u) * (int64_t)H + h] = a;
           }
+        } else {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) contrib[v] = fmaf(gate[u], acc[v][u], contrib[v]);
         }
       }
     }
-    if (mode != GRMX_FUSE_RETRIEVED && lane_in_group == 0 && h < H) {
-      if (mode == GRMX_FUSE_CONTRIB) {
-        out[bq * H + h] = contrib;
-      } else {
-        s_x[h] = online[bq * H + h] + contrib;
+    if constexpr (!kPerRoute) {
+#pragma unroll
+      for (int v = 0; v < kRows; ++v) {
+        const int h = (it0 + v) * groups + group;
+        float a = contrib[v];
+#pragma unroll
+        for (int o = G >> 1; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane_in_group == 0 && h < H) {
+          if (mode == GRMX_FUSE_CONTRIB) {
+            out[bq * H + h] = a;
+          } else {
+            s_x[h] = online[bq * H + h] + a;
+          }
+        }
       }
     }
   }
@@ -184,17 +222,44 @@ extern "C" int grmx_retrieve_fuse(const float* archive, const int64_t* indices, 
   const int VEC = vec ? 4 : 1;
   int G = 1;
   while (G < 32 && G * VEC < K) G <<= 1;
+  // fused modes: two steps over K per lane, i.e. fewer reduction steps per byte.  The per-route mode
+  // keeps one step per lane: its results are defined to equal gather followed by apply-query bit for bit.
+  if (mode != GRMX_FUSE_RETRIEVED && G >= 4 && K % (G / 2 * VEC) == 0) G >>= 1;
   const size_t smem = sizeof(float) * (size_t)(K + H);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint32_t* err = device_error_word_ptr();
+  const bool per_route = mode == GRMX_FUSE_RETRIEVED;
+#define GRMX_FUSE_LAUNCH(V, GG)                                                                                     \
+  do {                                                                                                              \
+    if (per_route) {                                                                                                \
+      retrieve_fuse_kernel<V, GG, true><<<static_cast<unsigned>(blocks), kThreads, smem, s>>>(                      \
+          archive, indices, gates, queries, online, ln_weight, ln_bias, ln_eps, static_cast<float*>(out), S, Q,     \
+          (int)R, (int)H, (int)K, mode, err);                                                                       \
+    } else {                                                                                                        \
+      retrieve_fuse_kernel<V, GG, false><<<static_cast<unsigned>(blocks), kThreads, smem, s>>>(                     \
+          archive, indices, gates, queries, online, ln_weight, ln_bias, ln_eps, static_cast<float*>(out), S, Q,     \
+          (int)R, (int)H, (int)K, mode, err);                                                                       \
+    }                                                                                                               \
+  } while (0)
   if (vec) {
-    retrieve_fuse_kernel<4><<<static_cast<unsigned>(blocks), kThreads, smem, s>>>(
-        archive, indices, gates, queries, online, ln_weight, ln_bias, ln_eps, static_cast<float*>(out),
-        S, Q, (int)R, (int)H, (int)K, G, mode, err);
+    switch (G) {
+      case 1: GRMX_FUSE_LAUNCH(4, 1); break;
+      case 2: GRMX_FUSE_LAUNCH(4, 2); break;
+      case 4: GRMX_FUSE_LAUNCH(4, 4); break;
+      case 8: GRMX_FUSE_LAUNCH(4, 8); break;
+      case 16: GRMX_FUSE_LAUNCH(4, 16); break;
+      default: GRMX_FUSE_LAUNCH(4, 32); break;
+    }
   } else {
-    retrieve_fuse_kernel<1><<<static_cast<unsigned>(blocks), kThreads, smem, s>>>(
-        archive, indices, gates, queries, online, ln_weight, ln_bias, ln_eps, static_cast<float*>(out),
-        S, Q, (int)R, (int)H, (int)K, G, mode, err);
+    switch (G) {
+      case 1: GRMX_FUSE_LAUNCH(1, 1); break;
+      case 2: GRMX_FUSE_LAUNCH(1, 2); break;
+      case 4: GRMX_FUSE_LAUNCH(1, 4); break;
+      case 8: GRMX_FUSE_LAUNCH(1, 8); break;
+      case 16: GRMX_FUSE_LAUNCH(1, 16); break;
+      default: GRMX_FUSE_LAUNCH(1, 32); break;
+    }
   }
+#undef GRMX_FUSE_LAUNCH
   return check_launch("retrieve_fuse");
 }

@@ -53,6 +53,7 @@ topk_route_kernel(const float* __restrict__ queries, const float* __restrict__ k
   }
   const float* qv = queries + bq * D;
   const float* kb = keys + b * (int64_t)S * D;
+  const bool vec4 = D % 4 == 0 && ((reinterpret_cast<uintptr_t>(queries) | reinterpret_cast<uintptr_t>(keys)) & 15u) == 0;
 
   for (int s = lane; s < S; s += 32) {
     float score;
@@ -61,7 +62,31 @@ topk_route_kernel(const float* __restrict__ queries, const float* __restrict__ k
     } else {
       const float* kr = kb + (int64_t)s * D;
       float acc = 0.0f;
-      for (int d = 0; d < D; ++d) acc = fmaf(__ldg(qv + d), __ldg(kr + d), acc);
+      if (vec4) {
+        // same sequential order over d as the scalar loop (the order is part of the contract), but
+        // the key row comes in 16-byte pieces, eight of them in flight before the first use
+        for (int d0 = 0; d0 < D; d0 += 32) {
+          float4 k4[8], q4[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (d0 + 4 * i < D) {
+              k4[i] = __ldg(reinterpret_cast<const float4*>(kr + d0) + i);
+              q4[i] = __ldg(reinterpret_cast<const float4*>(qv + d0) + i);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (d0 + 4 * i < D) {
+              acc = fmaf(q4[i].x, k4[i].x, acc);
+              acc = fmaf(q4[i].y, k4[i].y, acc);
+              acc = fmaf(q4[i].z, k4[i].z, acc);
+              acc = fmaf(q4[i].w, k4[i].w, acc);
+            }
+          }
+        }
+      } else {
+        for (int d = 0; d < D; ++d) acc = fmaf(__ldg(qv + d), __ldg(kr + d), acc);
+      }
       score = acc * scale;
     }
     sc[s] = score;
