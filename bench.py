@@ -188,15 +188,23 @@ def run_engine(args, rank, world, device):
         sets.append((k, v, q, torch.empty(rows, T, V, device=device, dtype=torch.bfloat16)))
     m_in = torch.zeros(rows, V, K, device=device, dtype=torch.float32)
     m_out = torch.empty_like(m_in)
-    # workspace that lets the kernel cut the 64 rows along T so that they fill the GPU
+    # One launch per step: with 64 rows on 148 SMs the kernel cuts every row along T into two pieces
+    # and the second piece derives its start state itself (pre-pass over the first piece's k and v).
+    # The variant with a caller workspace (piece-state kernel + scan, `--with-workspace`) is slower
+    # at this shape: two launches' worth of fixed cost.
     scratch_bytes = int(lib.grmx_chunk_scan_scratch_bytes(rows, T, K, V, cabi.BF16, cabi.F32))
     scratch = torch.empty(max(scratch_bytes, 16), device=device, dtype=torch.uint8)
 
     def step(i, stream):
         k, v, q, o = sets[i % n_sets]
-        cabi.check(lib.grmx_chunk_scan_fwd_ws(k.data_ptr(), v.data_ptr(), q.data_ptr(), m_in.data_ptr(),
-                                              o.data_ptr(), m_out.data_ptr(), rows, T, K, V, decay, cabi.BF16,
-                                              cabi.F32, cabi.PATH_AUTO, scratch.data_ptr(), scratch_bytes, stream))
+        if args.with_workspace:
+            cabi.check(lib.grmx_chunk_scan_fwd_ws(k.data_ptr(), v.data_ptr(), q.data_ptr(), m_in.data_ptr(),
+                                                  o.data_ptr(), m_out.data_ptr(), rows, T, K, V, decay, cabi.BF16,
+                                                  cabi.F32, cabi.PATH_AUTO, scratch.data_ptr(), scratch_bytes, stream))
+        else:
+            cabi.check(lib.grmx_chunk_scan_fwd(k.data_ptr(), v.data_ptr(), q.data_ptr(), m_in.data_ptr(),
+                                               o.data_ptr(), m_out.data_ptr(), rows, T, K, V, decay, cabi.BF16,
+                                               cabi.F32, cabi.PATH_AUTO, stream))
 
     sampler = ClockSampler(device.index)
     sampler.start()
@@ -275,7 +283,8 @@ def run_engine(args, rank, world, device):
         "gpu_launches": int(launches),
         "roofline": {
             "bound": "hbm",
-            "kernel": "linear-memory scan" + (" (piece-state kernel + scan kernel per step)" if kernels_per_step > 1.5 else ""),
+            "kernel": "linear-memory scan" + (" (piece-state kernel + scan kernel per step)" if kernels_per_step > 1.5
+                                              else " (one launch per step, rows cut along T inside the kernel)"),
             "achieved": achieved_gbs,
             "peak": hbm_peak,
             "unit": "GB/s",
@@ -492,6 +501,8 @@ def main(argv=None) -> int:
     parser.add_argument("--impl", choices=["engine", "reference"], default="engine")
     parser.add_argument("--skip-extras", action="store_true",
                         help="main workload only: no CPU baseline, no other workloads (small footprint for profiling)")
+    parser.add_argument("--with-workspace", action="store_true",
+                        help="time the two-kernel variant of the cut (piece-state kernel + scan over a caller workspace)")
     parser.add_argument("--full-occupancy-only", action="store_true",
                         help="run only the one-row-per-SM scan of the extras and print its figures (for profiling)")
     args = parser.parse_args(argv)

@@ -562,8 +562,7 @@ static bool prefer_sync_variant() {
 int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream) {
   const bool simple = p.T % kChunk == 0 && !p.reverse && !p.first_step_no_decay;
   if (scan_tcgen05_pipe_supported(p) && !(simple && prefer_sync_variant())) {
-    const int n_chunks = static_cast<int>((p.T + kChunk - 1) / kChunk);
-    return launch_scan_tcgen05_pipe(p, SplitInfo{1, n_chunks, nullptr}, stream);
+    return launch_scan_tcgen05_selfcut(p, stream);
   }
   if (p.K == 64 && p.H == 64) return launch<64, 64>(p, stream);
   return fail(GRMX_ERR_UNSUPPORTED, "tcgen05 scan: no kernel for d_k=%lld d_v=%lld", (long long)p.K,

@@ -146,7 +146,15 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const int T = static_cast<int>(p.T);
   const int total_chunks = (T + kChunk - 1) / kChunk;
   const int c_begin = piece * split.chunks_per_piece;
-  const int n_chunks = min(split.chunks_per_piece, total_chunks - c_begin);   // chunks of this CTA
+  const int n_chunks = min(split.chunks_per_piece, total_chunks - c_begin);   // chunks this CTA writes
+  // Without the states of the earlier pieces (split.partials == nullptr) the CTA derives its start
+  // state itself: a pre-pass over the `pre` chunks before its own runs only the state recurrence on
+  // them (k and v tiles, Vw, U, the register update) and none of the per-token work.  Local chunk
+  // index c covers pre-pass and own chunks alike, c = 0 .. n_all-1, global chunk g0 + c; the roles
+  // and barriers that exist only for own chunks count them as f = c - pre.
+  const int pre = (split.partials == nullptr) ? c_begin : 0;
+  const int n_all = pre + n_chunks;
+  const int g0 = c_begin - pre;
   const bool rev = p.reverse != 0;
   // Global chunk g covers processing steps [128g, 128g + len).  Forward, tile row r is step r of
   // the chunk; in a reverse scan the tile is still loaded in memory order, so row r is step
@@ -203,8 +211,11 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   if (!mbar_wait((bar), static_cast<uint32_t>(phase) & 1u, s_abort)) \
     break;
 
-  // Protocol.  Chunks are numbered locally, c = 0 .. n_chunks-1; "X(c)" is the completion of
-  // barrier X that belongs to chunk c (phase c/2 of X[c&1], phase c/3 of X[c%3]).  A waiter is
+  // Protocol.  Chunks are numbered locally, c = 0 .. n_all-1; "X(c)" is the completion of barrier
+  // X that belongs to chunk c (phase c/2 of X[c&1], phase c/3 of X[c%3]).  Barriers that only own
+  // chunks use (s_done, p_ready, a_done, buf_free, mb_ready, s_read, out_*) count f = c - pre instead;
+  // below, c stands for f on those.  A pre-pass chunk involves the loader, issuer B and the state
+  // group only, and the state group makes both arrivals on its stage_free.  A waiter is
   // never more than one completion behind, because the producer's next completion on the same
   // barrier needs something that comes after the waiter's wait:
   //   loader:   TMA of c    needs stage_free(c-3): one arrival after u_done(c-3) (state group), one
@@ -230,32 +241,34 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // ===================================================================== issuer A: [S | R]
     const uint32_t leader = elect_one();
     constexpr uint32_t idesc_sr = make_idesc(kChunk, kChunk + kD, 0, 0);
-    for (int c = 0; c < n_chunks; ++c) {
-      GRMX_WAIT(&bar_mb_ready[c % 3], c / 3)
+    for (int f = 0; f < n_chunks; ++f) {
+      const int c = pre + f;
+      GRMX_WAIT(&bar_mb_ready[f % 3], f / 3)
       GRMX_WAIT(&bar_full[c % kStages], c / kStages)
-      if (c >= 2) GRMX_WAIT(&bar_buf_free[c & 1], c / 2 - 1)
+      if (f >= 2) GRMX_WAIT(&bar_buf_free[f & 1], f / 2 - 1)
       tc_fence_after();
       const uint8_t* st = stage(c);
       const uint64_t dq = smem_desc(smem_u32(st + kStageQ), 16, 1024);
       const uint64_t dkm = smem_desc(smem_u32(st + kStageK), 16, 1024);   // 128 rows of k, then 64 of Mb
-      const uint32_t d_tmem = tmem_base + kColBuf + kBufCols * (c & 1);
+      const uint32_t d_tmem = tmem_base + kColBuf + kBufCols * (f & 1);
 #pragma unroll
       for (int kk = 0; kk < kD / 16; ++kk) {
         tc_mma_bf16_if(leader, d_tmem, desc_add(dq, kk * 32), desc_add(dkm, kk * 32), idesc_sr, kk > 0);
       }
-      tc_commit_if(leader, &bar_s_done[c & 1]);
+      tc_commit_if(leader, &bar_s_done[f & 1]);
     }
   } else if (warp == kLoader) {
     // ===================================================================== loader: TMA ring
     const uint32_t leader = elect_one();
     int loads_issued = 0;
-    for (int c = 0; c < n_chunks; ++c) {
+    for (int c = 0; c < n_all; ++c) {
       if (c >= kStages) GRMX_WAIT(&bar_stage_free[c % kStages], c / kStages - 1)
       uint8_t* st = stage(c);
       uint64_t* bar = &bar_full[c % kStages];
-      mbar_expect_tx_if(leader, bar, kTxBytes);
-      const int t0 = chunk_token0(c_begin + c);
-      tma_load_3d_if(leader, st + kStageQ, &map_q, bar, 0, t0, static_cast<int>(b));
+      const bool own = c >= pre;                      // the pre-pass needs no queries
+      mbar_expect_tx_if(leader, bar, own ? kTxBytes : 2 * kTileBytes);
+      const int t0 = chunk_token0(g0 + c);
+      if (own) tma_load_3d_if(leader, st + kStageQ, &map_q, bar, 0, t0, static_cast<int>(b));
       tma_load_3d_if(leader, st + kStageK, &map_k, bar, 0, t0, static_cast<int>(b));
       tma_load_3d_if(leader, st + kStageV, &map_v, bar, 0, t0, static_cast<int>(b));
       loads_issued = c + 1;
@@ -270,7 +283,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // ===================================================================== issuer B: U
     const uint32_t leader = elect_one();
     constexpr uint32_t idesc_u = make_idesc(kD, kD, 1, 1);
-    for (int c = 0; c < n_chunks; ++c) {
+    for (int c = 0; c < n_all; ++c) {
       GRMX_WAIT(&bar_vw_ready[c & 1], c / 2)
       if (c >= 2) GRMX_WAIT(&bar_u_free[c & 1], c / 2 - 1)
       tc_fence_after();
@@ -287,19 +300,20 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // ===================================================================== issuer C: A = P V
     const uint32_t leader = elect_one();
     constexpr uint32_t idesc_a = make_idesc(kChunk, kD, 0, 1);
-    for (int c = 0; c < n_chunks; ++c) {
-      GRMX_WAIT(&bar_p_ready[c & 1], c / 2)
+    for (int f = 0; f < n_chunks; ++f) {
+      const int c = pre + f;
+      GRMX_WAIT(&bar_p_ready[f & 1], f / 2)
       tc_fence_after();
       const uint64_t dv_mn = smem_desc(smem_u32(stage(c) + kStageV), kTileBytes, 1024);
-      const uint32_t buf = tmem_base + kColBuf + kBufCols * (c & 1);    // P: 16 tokens = 8 columns
+      const uint32_t buf = tmem_base + kColBuf + kBufCols * (f & 1);    // P: 16 tokens = 8 columns
 #pragma unroll
       for (int kk = 0; kk < kChunk / 16; ++kk) {
         tc_mma_bf16_ts_if(leader, buf + kColA, buf + 8u * kk, desc_add(dv_mn, kk * 2048), idesc_a, kk > 0);
       }
-      tc_commit_if(leader, &bar_a_done[c & 1]);
+      tc_commit_if(leader, &bar_a_done[f & 1]);
       // The next P pass is a whole chunk period away, so this warp has the time to see A_c finish
       // and to hand the stage back to the loader at once.
-      GRMX_WAIT(&bar_a_done[c & 1], c / 2)
+      GRMX_WAIT(&bar_a_done[f & 1], f / 2)
       if (leader) mbar_arrive(&bar_stage_free[c % kStages]);
     }
   }
@@ -327,7 +341,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       }
     };
     auto copy_chunk = [&](int c) {
-      const int g = c_begin + c;
+      const int g = g0 + c;
       const int len = chunk_len(g);
       const float w_v = step < len ? p.update_coeff * s_pow[len - 1 - step] : 0.0f;
       scaled_row_copy<4>(stage(c) + kStageV, vw_buf(c), row, w_v);
@@ -351,7 +365,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         for (int j = 0; j < kD; ++j) m[j] = owns_row ? src[j * p.m_col_stride] : 0.0f;
       }
       // pieces before this one: M <- decay^(tokens of piece q - offset) M + partial_q
-      for (int q = 0; q < piece; ++q) {
+      for (int q = 0; q < piece && split.partials != nullptr; ++q) {
         const int q_tokens = min(split.chunks_per_piece * kChunk, T - q * split.chunks_per_piece * kChunk);
         const float gq = powf(p.decay, static_cast<float>(q_tokens - first_offset(q * split.chunks_per_piece)));
         if (owns_row) {
@@ -371,26 +385,29 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           }
         }
       }
-      if (owns_row) write_mb(0);              // TMA never writes this part of a stage
-      fence_proxy_async();
-      mbar_arrive(&bar_mb_ready[0]);          // completion 0: the state before chunk 0
+      if (pre == 0) {
+        if (owns_row) write_mb(0);            // TMA never writes this part of a stage
+        fence_proxy_async();
+        mbar_arrive(&bar_mb_ready[0]);        // completion 0: the state before the first own chunk
+      }
     }
 
     do {
       GRMX_WAIT(&bar_full[0], 0)
       copy_chunk(0);
-      if (n_chunks > 1) {
+      if (n_all > 1) {
         GRMX_WAIT(&bar_full[1], 0)
         copy_chunk(1);
       }
-      for (int c = 0; c < n_chunks; ++c) {
-        const bool last = c + 1 == n_chunks;
+      for (int c = 0; c < n_all; ++c) {
+        const bool last = c + 1 == n_all;
         // ---- M_c = decay^len M_{c-1} + U_c ----
         GRMX_WAIT(&bar_u_done[c & 1], c / 2)
-        if (row == 0) mbar_arrive(&bar_stage_free[c % kStages]);
+        // a pre-pass chunk has no A product: both arrivals of its stage come from here
+        if (row == 0 || (row == 1 && c < pre)) mbar_arrive(&bar_stage_free[c % kStages]);
         tc_fence_after();
         {
-          const float carry = s_pow[chunk_len(c_begin + c) - first_offset(c_begin + c)];
+          const float carry = s_pow[chunk_len(g0 + c) - first_offset(g0 + c)];
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             uint32_t u[32];
@@ -403,9 +420,11 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         tc_fence_before();
         mbar_arrive(&bar_u_free[c & 1]);
         if (!last) {
-          if (owns_row) write_mb(c + 1);
-          fence_proxy_async();
-          mbar_arrive(&bar_mb_ready[(c + 1) % 3]);
+          if (c + 1 >= pre) {                 // the next chunk is an own chunk: [S | R] needs the state
+            if (owns_row) write_mb(c + 1);
+            fence_proxy_async();
+            mbar_arrive(&bar_mb_ready[(c + 1 - pre) % 3]);
+          }
         } else if (owns_row && p.memory_out != nullptr && piece + 1 == split.pieces) {
           float* m_out = static_cast<float*>(p.memory_out) + b * kD * kD + state_row * kD;
 #pragma unroll
@@ -419,7 +438,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           }
         }
         // ---- Vw of chunk c+2 into the buffer that U_c has read ----
-        if (c + 2 < n_chunks) {
+        if (c + 2 < n_all) {
           GRMX_WAIT(&bar_full[(c + 2) % kStages], (c + 2) / kStages)
           copy_chunk(c + 2);
         }
@@ -442,9 +461,9 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       // columns) lands on S columns 16*blk .. 16*blk+15: group 0 overwrites S block 0 after
       // reading it; group 1 overwrites S block 1, which group 0 reads second, and waits for
       // s_read(c) before it stores.
-      for (int c = 0; c < n_chunks; ++c) {
-        const uint32_t buf_row = lane_base + kBufCols * (c & 1);
-        GRMX_WAIT(&bar_s_done[c & 1], c / 2)
+      for (int f = 0; f < n_chunks; ++f) {
+        const uint32_t buf_row = lane_base + kBufCols * (f & 1);
+        GRMX_WAIT(&bar_s_done[f & 1], f / 2)
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
@@ -457,7 +476,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
           }
           if (g == 0 && k == 1) {
             tc_fence_before();
-            mbar_arrive(&bar_s_read[c & 1]);
+            mbar_arrive(&bar_s_read[f & 1]);
           }
           if (nz) {
             const int m0 = 127 - row + 32 * blk;            // reversed-table index of column 32*blk
@@ -473,14 +492,14 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             for (int t = 0; t < 16; ++t) pk[t] = 0u;
           }
           if (g == 1 && k == 0) {
-            GRMX_WAIT(&bar_s_read[c & 1], c / 2)
+            GRMX_WAIT(&bar_s_read[f & 1], f / 2)
           }
           tc_st16_async(buf_row + 16u * blk, pk);
         }
         if (*s_abort) break;
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&bar_p_ready[c & 1]);
+        mbar_arrive(&bar_p_ready[f & 1]);
       }
     } else {
       // ---- epilogue groups: group 2+h writes the output columns 32h .. 32h+31 ----
@@ -495,7 +514,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         const uint32_t buf_row = lane_base + kBufCols * (e & 1);
         GRMX_WAIT(&bar_a_done[e & 1], e / 2)
         tc_fence_after();
-        const int ge = c_begin + e;
+        const int ge = c_begin + e;           // global chunk (own chunks start at c_begin whatever the pre-pass)
         const bool row_live = step < chunk_len(ge);
         const float r_scale = row_live ? p.hidden_scale * s_pow[step + 1 - first_offset(ge)] : 0.0f;
         const int t0 = chunk_token0(ge);

@@ -19,6 +19,8 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "scan.cuh"
@@ -251,6 +253,18 @@ int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p) {
   return p.B * (split.pieces - 1) * split.subs * kD * kD * static_cast<int64_t>(sizeof(float));
 }
 
+int launch_scan_tcgen05_selfcut(const ScanParams& p, cudaStream_t stream) {
+  static const bool disabled = [] {
+    const char* env = getenv("GRMX_SCAN_CUT");
+    return env != nullptr && strcmp(env, "off") == 0;
+  }();
+  SplitInfo split = plan_split(p);
+  if (disabled) split = SplitInfo{1, static_cast<int>((p.T + kChunk - 1) / kChunk), nullptr, 1};
+  split.partials = nullptr;
+  split.subs = 1;
+  return launch_scan_tcgen05_pipe(p, split, stream);
+}
+
 int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
   const int64_t n_chunks = (p.T + kChunk - 1) / kChunk;
   SplitInfo split = plan_split(p);
@@ -258,7 +272,7 @@ int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratc
   const int64_t need = p.B * (pieces - 1) * split.subs * kD * kD * static_cast<int64_t>(sizeof(float));
   if (pieces <= 1 || scratch == nullptr || scratch_bytes < need ||
       (reinterpret_cast<uintptr_t>(scratch) & 15u) != 0) {
-    return launch_scan_tcgen05_pipe(p, SplitInfo{1, static_cast<int>(n_chunks), nullptr}, stream);
+    return launch_scan_tcgen05_selfcut(p, stream);
   }
   split.partials = static_cast<const float*>(scratch);
 

@@ -27,21 +27,6 @@ __device__ __forceinline__ void load_row_chunk(const float* p, float (&out)[VEC]
   }
 }
 
-__device__ __forceinline__ float block_sum(float v, float* s_red) {
-  // fixed-order reduction: warp shuffles, then warp 0 adds the 8 partials
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  __syncthreads();
-  if (lane == 0) s_red[warp] = v;
-  __syncthreads();
-  float total = 0.0f;
-#pragma unroll
-  for (int w = 0; w < kThreads / 32; ++w) total += s_red[w];
-  return total;
-}
-
 // VEC floats per load, G lanes per matrix row (G * VEC divides into K in whole steps or covers it
 // once), kPerRoute: the per-route products are the result (mode "retrieved"); otherwise the gate
 // weights are applied lane by lane before the one reduction per row.
@@ -58,7 +43,6 @@ retrieve_fuse_kernel(const float* __restrict__ archive, const int64_t* __restric
   float* s_x = s_mem + K;         // [H]
   __shared__ int64_t s_idx[kMaxRoutes];
   __shared__ float s_gate[kMaxRoutes];
-  __shared__ float s_red[kThreads / 32];
   __shared__ int s_live;
 
   const int64_t bq = blockIdx.x;
@@ -177,17 +161,24 @@ retrieve_fuse_kernel(const float* __restrict__ archive, const int64_t* __restric
     for (int h = threadIdx.x; h < H; h += kThreads) out[bq * H + h] = online[bq * H + h];
     return;
   }
+  // LayerNorm over the H values of the row by the first warp alone (fixed-order shuffles): the other
+  // warps are done and free their slots instead of waiting at four more CTA barriers
+  if (threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
   float part = 0.0f;
-  for (int h = threadIdx.x; h < H; h += kThreads) part += s_x[h];
-  const float mean = block_sum(part, s_red) / (float)H;
+  for (int h = lane; h < H; h += 32) part += s_x[h];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  const float mean = part / (float)H;
   part = 0.0f;
-  for (int h = threadIdx.x; h < H; h += kThreads) {
+  for (int h = lane; h < H; h += 32) {
     const float d = s_x[h] - mean;
     part = fmaf(d, d, part);
   }
-  const float var = block_sum(part, s_red) / (float)H;
-  const float rstd = rsqrtf(var + ln_eps);
-  for (int h = threadIdx.x; h < H; h += kThreads) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  const float rstd = rsqrtf(part / (float)H + ln_eps);
+  for (int h = lane; h < H; h += 32) {
     float y = (s_x[h] - mean) * rstd;
     if (ln_weight != nullptr) y *= ln_weight[h];
     if (ln_bias != nullptr) y += ln_bias[h];

@@ -35,7 +35,8 @@ struct SplitInfo {
   int pieces;              // CTAs per batch row
   int chunks_per_piece;    // 128-token chunks handled by each of them
   const float* partials;   // [B, pieces-1, subs, H, K] fp32: local state contribution of pieces
-                           // 0..pieces-2, each as the sum of `subs` terms (computed by separate CTAs)
+                           // 0..pieces-2, each as the sum of `subs` terms (computed by separate CTAs);
+                           // nullptr with pieces > 1: every piece derives its start state itself
   int subs = 1;
 };
 
@@ -47,5 +48,9 @@ int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaSt
 // the shape is not covered), and the launch that runs the piece-state kernel followed by the scan.
 int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p);
 int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
+// The same cut without a workspace: one launch, every piece derives its start state itself with a
+// pre-pass over the chunks before its own (state recurrence only).  Falls back to the uncut scan
+// when a cut does not apply.
+int launch_scan_tcgen05_selfcut(const ScanParams& p, cudaStream_t stream);
 
 }  // namespace grmx
