@@ -82,6 +82,10 @@ int64_t grmx_launch_count(void);
  * memory_out [B,H,K] in state_dtype (GRMX_F32, or equal to io_dtype).
  * T == 0 copies memory_in to memory_out and writes no hidden.
  * path selects the kernel family (GRMX_PATH_*).
+ * With few batch rows and many tokens the tensor-core path cuts every row along T into up to
+ * four pieces that run on different SMs; each piece derives the state it starts from by running
+ * the state recurrence alone over the tokens before it (one launch, no workspace; set
+ * GRMX_SCAN_CUT=off in the environment to keep rows whole).
  *
  * Replaces grm_cuda::chunk_update_forward (grm/csrc/bindings.cpp:6,
  * grm/csrc/chunk_update.cu:523-586; math grm/core/cuda_ops.py:218-254,
@@ -93,10 +97,12 @@ int grmx_chunk_scan_fwd(const void* keys, const void* values, const void* querie
                         int io_dtype, int state_dtype, int path, void* stream);
 
 /*
- * grmx_chunk_scan_fwd with a caller-provided workspace.  When a call has few batch rows and
- * many tokens the tensor-core path can cut every row along T into pieces that run on different
- * SMs; the pieces exchange their local state contributions through `scratch` (device memory,
- * 16-byte aligned, contents irrelevant on entry, not preserved).
+ * grmx_chunk_scan_fwd with a caller-provided workspace: the two-kernel form of the cut along T.
+ * A first kernel computes every piece's own contribution to the state into `scratch` (device
+ * memory, 16-byte aligned, contents irrelevant on entry, not preserved), the scan kernel rebuilds
+ * each piece's start state from them.  More pieces than the one-launch form allows (no piece
+ * repeats the work of another), at the price of a second launch: the better choice for very
+ * long rows.
  * grmx_chunk_scan_scratch_bytes returns the size that cut needs for the given call on the
  * current device, or 0 when the call would not be cut.  With scratch == NULL or a buffer that
  * is too small the call behaves exactly like grmx_chunk_scan_fwd.  Results are the same up to

@@ -145,8 +145,9 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   const int piece = static_cast<int>(blockIdx.x / p.B);
   const int T = static_cast<int>(p.T);
   const int total_chunks = (T + kChunk - 1) / kChunk;
-  const int c_begin = piece * split.chunks_per_piece;
-  const int n_chunks = min(split.chunks_per_piece, total_chunks - c_begin);   // chunks this CTA writes
+  const int c_begin = split.use_starts ? split.starts[piece] : piece * split.chunks_per_piece;
+  const int n_chunks = split.use_starts ? split.starts[piece + 1] - c_begin
+                                        : min(split.chunks_per_piece, total_chunks - c_begin);   // chunks this CTA writes
   // Without the states of the earlier pieces (split.partials == nullptr) the CTA derives its start
   // state itself: a pre-pass over the `pre` chunks before its own runs only the state recurrence on
   // them (k and v tiles, Vw, U, the register update) and none of the per-token work.  Local chunk

@@ -253,6 +253,42 @@ int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p) {
   return p.B * (split.pieces - 1) * split.subs * kD * kD * static_cast<int64_t>(sizeof(float));
 }
 
+namespace {
+
+// Piece boundaries for the cut without a workspace.  Piece q runs the state recurrence alone over the
+// chunks before it (cost kPrepassCost per chunk, measured relative to a full chunk) and then its own
+// chunks, so equal pieces would leave the last one finishing long after the first.  Boundaries are
+// chosen so that all pieces take about the same time: own(q) = own(0) - kPrepassCost * begin(q).
+void balance_pieces(SplitInfo* split, int64_t n_chunks) {
+  constexpr double kPrepassCost = 0.54;
+  const int pieces = split->pieces;
+  auto end_of = [&](double first) {         // where the last piece ends if piece 0 owns `first` chunks
+    double begin = 0.0;
+    for (int q = 0; q < pieces; ++q) begin += std::max(first - kPrepassCost * begin, 0.0);
+    return begin;
+  };
+  double lo = 0.0, hi = static_cast<double>(n_chunks);
+  for (int it = 0; it < 60; ++it) {
+    const double mid = 0.5 * (lo + hi);
+    (end_of(mid) < static_cast<double>(n_chunks) ? lo : hi) = mid;
+  }
+  const double first = hi;
+  double begin = 0.0;
+  split->starts[0] = 0;
+  for (int q = 0; q < pieces; ++q) {
+    begin += std::max(first - kPrepassCost * begin, 0.0);
+    int edge = static_cast<int>(std::lround(begin));
+    // every piece owns at least one chunk, and enough chunks are left for the pieces behind it
+    edge = std::max(edge, split->starts[q] + 1);
+    edge = std::min<int64_t>(edge, n_chunks - (pieces - 1 - q));
+    split->starts[q + 1] = edge;
+  }
+  split->starts[pieces] = static_cast<int>(n_chunks);
+  split->use_starts = 1;
+}
+
+}  // namespace
+
 int launch_scan_tcgen05_selfcut(const ScanParams& p, cudaStream_t stream) {
   static const bool disabled = [] {
     const char* env = getenv("GRMX_SCAN_CUT");
@@ -262,6 +298,10 @@ int launch_scan_tcgen05_selfcut(const ScanParams& p, cudaStream_t stream) {
   if (disabled) split = SplitInfo{1, static_cast<int>((p.T + kChunk - 1) / kChunk), nullptr, 1};
   split.partials = nullptr;
   split.subs = 1;
+  // Beyond four pieces the pre-pass of the last piece (more than half of the row) sets the time, and
+  // every further piece only re-reads k and v once more.
+  split.pieces = std::min(split.pieces, 4);
+  if (split.pieces > 1) balance_pieces(&split, (p.T + kChunk - 1) / kChunk);
   return launch_scan_tcgen05_pipe(p, split, stream);
 }
 

@@ -38,6 +38,11 @@ struct SplitInfo {
                            // 0..pieces-2, each as the sum of `subs` terms (computed by separate CTAs);
                            // nullptr with pieces > 1: every piece derives its start state itself
   int subs = 1;
+  // Uneven pieces (only without partials): piece q owns chunks [starts[q], starts[q+1]).  A piece
+  // that derives its own start state pays for every chunk before it, so later pieces are shorter.
+  static constexpr int kMaxPieces = 64;
+  int use_starts = 0;
+  int starts[kMaxPieces + 1] = {0};
 };
 
 // Warp-specialised variant of the tcgen05 scan (d_k = d_v = 64); same coverage rules otherwise.
