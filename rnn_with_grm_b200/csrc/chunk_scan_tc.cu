@@ -516,14 +516,13 @@ bool scan_tcgen05_supported(const ScanParams& p, int io_dtype, int state_dtype, 
     *why = "needs bf16 tokens and an fp32 state";
     return false;
   }
-  if (!(p.K == 64 && p.H == 64)) {
-    *why = "d_k and d_v must both be 64";
+  if (!scan_tcgen05_pipe_supported(p)) {
+    *why = "d_k and d_v must be multiples of 64 (d_k <= 1024, d_v <= 4096)";
     return false;
   }
   // the pipelined kernel takes any T, either direction; the single-warpgroup one only whole chunks
-  const bool simple = p.T % kChunk == 0 && !p.reverse && !p.first_step_no_decay;
-  if (p.T < 1 || (!simple && !scan_tcgen05_pipe_supported(p))) {
-    *why = "this head size needs T to be a multiple of 128 and a forward scan";
+  if (p.T < 1) {
+    *why = "no tokens";
     return false;
   }
   if (p.B > 0x7fffffffLL || p.T > 0x7fff0000LL) {
@@ -560,7 +559,7 @@ static bool prefer_sync_variant() {
 }
 
 int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream) {
-  const bool simple = p.T % kChunk == 0 && !p.reverse && !p.first_step_no_decay;
+  const bool simple = p.K == 64 && p.H == 64 && p.T % kChunk == 0 && !p.reverse && !p.first_step_no_decay;
   if (scan_tcgen05_pipe_supported(p) && !(simple && prefer_sync_variant())) {
     return launch_scan_tcgen05_selfcut(p, stream);
   }

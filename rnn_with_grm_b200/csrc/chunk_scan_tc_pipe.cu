@@ -111,7 +111,7 @@ __device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { re
 __global__ void __launch_bounds__(kThreads, 1)
 linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
-                           ScanParams p, SplitInfo split,
+                           ScanParams p, SplitInfo split, int x_k, int accumulate_out,
                            uint32_t* error_word) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -141,8 +141,16 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   // CTA per (piece, row), piece-major.  Piece q > 0 starts from the state that the pieces before it
   // leave behind, rebuilt in its prologue from memory_in and their local contributions in
   // `split.partials` (written by the piece-state kernel that runs before this one).
-  const int64_t b = blockIdx.x % p.B;
-  const int piece = static_cast<int>(blockIdx.x / p.B);
+  // Heads wider than 64 run as 64 x 64 blocks of the state, which are independent recurrences:
+  // block (vb, a) scans the value features 64vb.. against the key/query features x_k = 64a.., and the
+  // outputs of the blocks of one vb add up (one launch per a; launches after the first add to what
+  // is there).  The value block is the fastest index of the grid, so the CTAs that read the same
+  // q and k tiles are neighbours in time and share them through L2.
+  const int n_vb = static_cast<int>(p.H / kD);
+  const int vb = static_cast<int>(blockIdx.x % n_vb);
+  const int64_t b = (blockIdx.x / n_vb) % p.B;
+  const int piece = static_cast<int>(blockIdx.x / n_vb / p.B);
+  const int x_v = vb * kD;
   const int T = static_cast<int>(p.T);
   const int total_chunks = (T + kChunk - 1) / kChunk;
   const int c_begin = split.use_starts ? split.starts[piece] : piece * split.chunks_per_piece;
@@ -269,9 +277,9 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       const bool own = c >= pre;                      // the pre-pass needs no queries
       mbar_expect_tx_if(leader, bar, own ? kTxBytes : 2 * kTileBytes);
       const int t0 = chunk_token0(g0 + c);
-      if (own) tma_load_3d_if(leader, st + kStageQ, &map_q, bar, 0, t0, static_cast<int>(b));
-      tma_load_3d_if(leader, st + kStageK, &map_k, bar, 0, t0, static_cast<int>(b));
-      tma_load_3d_if(leader, st + kStageV, &map_v, bar, 0, t0, static_cast<int>(b));
+      if (own) tma_load_3d_if(leader, st + kStageQ, &map_q, bar, x_k, t0, static_cast<int>(b));
+      tma_load_3d_if(leader, st + kStageK, &map_k, bar, x_k, t0, static_cast<int>(b));
+      tma_load_3d_if(leader, st + kStageV, &map_v, bar, x_v, t0, static_cast<int>(b));
       loads_issued = c + 1;
     }
     if (*s_abort) {
@@ -352,8 +360,8 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
 
     // state at the start of this CTA's chunks
     {
-      const float* m_in = static_cast<const float*>(p.memory_in) + b * kD * kD;
-      const float* src = m_in + state_row * p.m_row_stride;
+      const float* m_in = static_cast<const float*>(p.memory_in) + b * p.H * p.K;
+      const float* src = m_in + (x_v + state_row) * p.m_row_stride + x_k * p.m_col_stride;
       const bool vec = p.m_col_stride == 1 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
       if (owns_row && vec) {
 #pragma unroll
@@ -427,7 +435,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
             mbar_arrive(&bar_mb_ready[(c + 1 - pre) % 3]);
           }
         } else if (owns_row && p.memory_out != nullptr && piece + 1 == split.pieces) {
-          float* m_out = static_cast<float*>(p.memory_out) + b * kD * kD + state_row * kD;
+          float* m_out = static_cast<float*>(p.memory_out) + b * p.H * p.K + (x_v + state_row) * p.K + x_k;
 #pragma unroll
           for (int j = 0; j < kD; j += 4) {
             float4 o;
@@ -545,18 +553,29 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
               o[i] = fmaf(r_scale, __uint_as_float(rv[ch * 8 + i]), __uint_as_float(av[ch * 8 + i]));
             }
             uint4 w;
+            const int piece16 = 2 * half + ch;              // 16-byte piece of the 64-byte half row
+            __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(p.hidden_out) +
+                                     (b * p.T + static_cast<int64_t>(t0) + row) * p.H + x_v + 32 * h + piece16 * 8;
+            if (accumulate_out && row_live) {
+              // a later key/query block of a wide head: add to the sum of the blocks before it
+              const uint4 prev = *reinterpret_cast<const uint4*>(out_row);
+              const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&prev);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(pp[i]);
+                o[2 * i] += f.x;
+                o[2 * i + 1] += f.y;
+              }
+            }
             w.x = pack_bf16(o[0], o[1]);
             w.y = pack_bf16(o[2], o[3]);
             w.z = pack_bf16(o[4], o[5]);
             w.w = pack_bf16(o[6], o[7]);
-            const int piece16 = 2 * half + ch;              // 16-byte piece of the 64-byte half row
             if (by_tma) {
               // 64-byte rows, 64-byte swizzle: piece j of row r sits at position j ^ ((r >> 1) & 3)
               *reinterpret_cast<uint4*>(s_out + row * 64 + ((piece16 ^ ((row >> 1) & 3)) * 16)) = w;
             } else if (row_live) {
-              __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.hidden_out) +
-                                   (b * p.T + static_cast<int64_t>(t0) + row) * kD + 32 * h;
-              *reinterpret_cast<uint4*>(out + piece16 * 8) = w;
+              *reinterpret_cast<uint4*>(out_row) = w;
             }
           }
         }
@@ -565,7 +584,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         if (row == 0) {
           GRMX_WAIT(&bar_out_ready[h], e)
           if (by_tma) {
-            tma_store_3d(s_out, &map_o, 32 * h, t0, static_cast<int>(b));
+            tma_store_3d(s_out, &map_o, x_v + 32 * h, t0, static_cast<int>(b));
             bulk_commit();
           }
         }
@@ -587,7 +606,9 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
 
 }  // namespace
 
-bool scan_tcgen05_pipe_supported(const ScanParams& p) { return p.K == kD && p.H == kD; }
+bool scan_tcgen05_pipe_supported(const ScanParams& p) {
+  return p.K % kD == 0 && p.H % kD == 0 && p.K >= kD && p.H >= kD && p.K <= 1024 && p.H <= 4096;
+}
 
 int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaStream_t stream) {
   static std::mutex mutex;
@@ -608,13 +629,20 @@ int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaSt
                 cudaGetErrorString(attr_status));
   }
   CUtensorMap map_q, map_k, map_v, map_o;
-  if (!make_token_map(&map_q, p.queries, p.B, p.T, kD) || !make_token_map(&map_k, p.keys, p.B, p.T, kD) ||
-      !make_token_map(&map_v, p.values, p.B, p.T, kD) || !make_token_half_map(&map_o, p.hidden_out, p.B, p.T, kD)) {
+  if (!make_token_map(&map_q, p.queries, p.B, p.T, p.K) || !make_token_map(&map_k, p.keys, p.B, p.T, p.K) ||
+      !make_token_map(&map_v, p.values, p.B, p.T, p.H) || !make_token_half_map(&map_o, p.hidden_out, p.B, p.T, p.H)) {
     return fail(GRMX_ERR_LAUNCH, "tcgen05 scan: cuTensorMapEncodeTiled failed");
   }
-  linear_scan_tc_pipe_kernel<<<static_cast<unsigned>(p.B * split.pieces), kThreads, kSmemAlloc, stream>>>(
-      map_q, map_k, map_v, map_o, p, split, device_error_word_ptr());
-  return check_launch("linear_scan_tcgen05_pipe");
+  // one launch per 64-wide block of key/query features; the blocks of value features are in the grid
+  const int64_t blocks = p.B * split.pieces * (p.H / kD);
+  if (blocks > 0x7fffffffLL) return fail(GRMX_ERR_UNSUPPORTED, "tcgen05 scan: grid too large");
+  for (int x_k = 0; x_k < static_cast<int>(p.K); x_k += kD) {
+    linear_scan_tc_pipe_kernel<<<static_cast<unsigned>(blocks), kThreads, kSmemAlloc, stream>>>(
+        map_q, map_k, map_v, map_o, p, split, x_k, x_k > 0 ? 1 : 0, device_error_word_ptr());
+    const int rc = check_launch("linear_scan_tcgen05_pipe");
+    if (rc != GRMX_OK) return rc;
+  }
+  return GRMX_OK;
 }
 
 }  // namespace grmx

@@ -217,8 +217,9 @@ int pick_pieces(const ScanParams& p) {
   if (!scan_tcgen05_pipe_supported(p)) return 1;
   const int64_t n_chunks = (p.T + kChunk - 1) / kChunk;
   const int sms = sm_count_of_current_device();
+  const int64_t ctas_per_piece = p.B * (p.H / kD);     // one CTA per row and 64-wide block of value features
   int pieces = 1;
-  while (p.B * pieces * 2 <= sms && n_chunks / (pieces * 2) >= 2) pieces *= 2;
+  while (ctas_per_piece * pieces * 2 <= sms && n_chunks / (pieces * 2) >= 2) pieces *= 2;
   return pieces;
 }
 
@@ -248,6 +249,7 @@ SplitInfo plan_split(const ScanParams& p) {
 }  // namespace
 
 int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p) {
+  if (p.K != kD || p.H != kD) return 0;                // the two-kernel cut exists for 64 x 64 heads only
   const SplitInfo split = plan_split(p);
   if (split.pieces <= 1) return 0;
   return p.B * (split.pieces - 1) * split.subs * kD * kD * static_cast<int64_t>(sizeof(float));
@@ -310,7 +312,7 @@ int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratc
   SplitInfo split = plan_split(p);
   const int pieces = split.pieces;
   const int64_t need = p.B * (pieces - 1) * split.subs * kD * kD * static_cast<int64_t>(sizeof(float));
-  if (pieces <= 1 || scratch == nullptr || scratch_bytes < need ||
+  if (pieces <= 1 || p.K != kD || p.H != kD || scratch == nullptr || scratch_bytes < need ||
       (reinterpret_cast<uintptr_t>(scratch) & 15u) != 0) {
     return launch_scan_tcgen05_selfcut(p, stream);
   }

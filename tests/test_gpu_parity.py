@@ -370,7 +370,7 @@ def test_tcgen05_scan_is_linear_in_values_and_state():
 
 def test_tcgen05_path_refuses_what_it_does_not_cover():
     k, v, q, m = make_chunk(1, 1, 100, 32, 64)
-    with pytest.raises(cabi.GrmxError, match="must both be 64"):
+    with pytest.raises(cabi.GrmxError, match="multiples of 64"):
         gx.chunk_scan_fwd(dev(k, torch.bfloat16), dev(v, torch.bfloat16), dev(q, torch.bfloat16), dev(m), 0.97,
                           cabi.PATH_TCGEN05)
     with pytest.raises(cabi.GrmxError, match="bf16"):
@@ -416,6 +416,26 @@ def test_tcgen05_backward_through_three_scans():
     got = gx.chunk_scan_bwd(tgh, dev(gm), tk, tv, tq, dev(m), 0.97, cabi.PATH_TCGEN05)
     for a, b in zip(got, want):
         close(a, b, LOWP_TOL)
+
+
+@pytest.mark.parametrize("B,T,K,H", [(2, 300, 64, 128), (2, 512, 128, 128), (1, 640, 64, 512), (3, 256, 128, 64),
+                                     (150, 256, 128, 128), (2, 1024, 192, 64)])
+def test_tcgen05_scan_wide_heads_run_as_blocks(B, T, K, H):
+    """Heads wider than 64 are scanned as 64 x 64 blocks of the state; the outputs of the key/query
+    blocks are summed in the bf16 output (one more rounding per block), the state is exact per block."""
+    k, v, q, m = make_chunk(K + H + T, B, T, K, H)
+    tk, tv, tq = dev(k, torch.bfloat16), dev(v, torch.bfloat16), dev(q, torch.bfloat16)
+    want_h, want_m = go.chunk_update_sequential(host(tk), host(tv), host(tq), m, 0.97)
+    hidden, m_out = gx.chunk_scan_fwd(tk, tv, tq, dev(m), 0.97, cabi.PATH_TCGEN05)
+    close(hidden, want_h, LOWP_TOL)
+    close(m_out, want_m, LOWP_TOL)
+    assert cabi.device_error_word() == 0
+    # the general form as well: reverse order, no decay on the first step, transposed start state
+    want = go.linear_scan(host(tk), host(tv), host(tq), m, 0.93, update_coeff=0.31, hidden_scale=1.7,
+                          memory_out_scale=0.6, reverse=True, first_step_no_decay=True)
+    got_h, got_m = gx.linear_scan(tk, tv, tq, dev(m), 0.93, 0.31, 1.7, 0.6, True, True, cabi.PATH_TCGEN05)
+    close(got_h, want[0], LOWP_TOL)
+    close(got_m, want[1], LOWP_TOL)
 
 
 @pytest.mark.parametrize("B,T", [(1, 2048), (8, 2048), (64, 2048), (3, 1000), (16, 517), (2, 32768)])

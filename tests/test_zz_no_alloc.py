@@ -70,7 +70,7 @@ def test_static_workspace_scan_refuses_what_it_cannot_hold():
     # d_k = 32 is outside what the tensor-core scan covers: refused, nothing runs
     rc = lib.grmx_chunk_scan_fwd_static(cabi.ptr(k), cabi.ptr(v), cabi.ptr(q), cabi.ptr(m), cabi.ptr(v), cabi.ptr(m),
                                         2, 256, 32, 64, 0.97, cabi.current_stream())
-    assert rc == 2 and b"must both be 64" in lib.grmx_last_error()
+    assert rc == 2 and b"multiples of 64" in lib.grmx_last_error()
     # a call that needs no cut still works (it simply does not touch the workspace)
     got_h, got_m = _static_call(k, v, q, m, 0.97)
     want_h, want_m = gx.chunk_scan_fwd(k, v, q, m, 0.97, cabi.PATH_TCGEN05)
