@@ -290,9 +290,10 @@ def run_engine(args, rank, world, device):
             "unit": "GB/s",
             "frac": achieved_gbs / hbm_peak,
             "peak_source": peak_kind,
-            # DRAM bytes of one step from the ncu capture of this workload (profiles/): scan kernel
-            # 53.6 MB read + 2.4 MB written, piece-state kernel 16.8 MB read
-            "traffic": 72783616 if kernels_per_step > 1.5 else None,
+            # DRAM bytes of one step from the ncu captures of this workload (profiles/).  One launch:
+            # 51.5 MB read + 1.9 MB written (the output is still in L2 when the kernel ends).  Two-kernel
+            # cut: scan 53.6 MB read + 2.4 MB written, piece-state kernel 16.8 MB read.
+            "traffic": 72783616 if kernels_per_step > 1.5 else 53354240,
             "algorithmic_bytes_per_launch": algo_bytes,
             "launch_ms": launch_ms,
             "tensor_tflops": algo_flops / (launch_ms * 1e-3) / 1e12,

@@ -95,7 +95,11 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> chunk_update_forward_cuda(
   const int io = dtype_code(k.scalar_type(), "keys");
   const int st = dtype_code(m.scalar_type(), "memory");
   // few rows, many tokens: give the kernel a workspace so it can cut the rows along T
-  const int64_t scratch_bytes = g_scan_path.load() == GRMX_PATH_FFMA ? 0 : grmx_chunk_scan_scratch_bytes(B, T, K, H, io, st);
+  // Few rows and many tokens: the scan is cut along T.  Up to four pieces the library does that in one
+  // launch without a workspace; the two-kernel form over a workspace pays when the call allows more
+  // pieces than that, i.e. when the workspace holds five or more piece states per row.
+  int64_t scratch_bytes = g_scan_path.load() == GRMX_PATH_FFMA ? 0 : grmx_chunk_scan_scratch_bytes(B, T, K, H, io, st);
+  if (scratch_bytes < 5 * B * H * K * static_cast<int64_t>(sizeof(float))) scratch_bytes = 0;
   at::Tensor scratch;
   if (scratch_bytes > 0) scratch = at::empty({scratch_bytes}, k.options().dtype(at::kByte));
   check_status(grmx_chunk_scan_fwd_ws(k.data_ptr(), v.data_ptr(), q.data_ptr(), m.data_ptr(),
