@@ -42,6 +42,7 @@ if str(ROOT) not in sys.path:
 
 CFG2 = dict(B=8, Hd=8, T=2048, K=64, V=64, decay=0.97)
 CFG3 = dict(B=16, Hd=8, T=8192, segment=256, K=64, V=64, top_k=4)
+CFG4 = dict(B=8, T=8192, layers=4, hidden=512, K=64, segment=512, top_k=4, vocab=32768, decay=0.97)
 CFG5_SLAB = dict(rows=256, T=32768, K=128, V=128, decay=0.97)   # 256 of the 4096 (b,h) rows of config 5
 L2_BYTES = 126 * 1024 * 1024
 
@@ -341,12 +342,54 @@ def full_occupancy_scan(lib, device, hbm_peak, launches=5):
             "bytes": nbytes, "row_tokens_per_s": rows * T / (ms * 1e-3)}
 
 
+def config4_model(device):
+    """Config 4 end to end: the four-layer segment-memory language model (hidden 512, d_k 64, segment
+    512, top-k 4, vocabulary 32768) over 8 x 8192 token ids, bf16 activations with fp32 state, run by
+    the package's own segment loop with random weights under the reference's parameter names.  The
+    figure includes the projections (cuBLAS) and the 512 -> 32768 output layer."""
+    from rnn_with_grm_b200.segment_memory import StackedSegmentMemoryRunner, language_model_parameter_shapes
+
+    c4 = CFG4
+    g = torch.Generator(device=device).manual_seed(4)
+    params = {}
+    for name, shape in language_model_parameter_shapes(c4["layers"], c4["hidden"], c4["K"], c4["vocab"], c4["hidden"]).items():
+        if name.endswith("layer_norm.weight"):
+            t = torch.ones(shape, device=device)
+        elif len(shape) == 2 and "embedding" not in name:
+            t = (torch.rand(shape, device=device, generator=g) * 2 - 1) * (6.0 / sum(shape)) ** 0.5
+        elif "embedding" in name:
+            t = torch.randn(shape, device=device, generator=g)
+        else:
+            t = torch.zeros(shape, device=device)
+        params[name] = t.to(torch.bfloat16)
+    runner = StackedSegmentMemoryRunner(params, c4["layers"], language_model=True, segment_length=c4["segment"],
+                                        retrieval_top_k=c4["top_k"], memory_capacity_segments=16, memory_decay=c4["decay"])
+    ids = torch.randint(0, c4["vocab"], (c4["B"], c4["T"]), device=device, generator=g)
+    for _ in range(2):
+        logits, _ = runner.forward(ids, reset_memory=True)
+    del logits
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    e0.record()
+    for _ in range(reps):
+        logits, _ = runner.forward(ids, reset_memory=True)
+        del logits
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    return {"ms": ms, "tokens_per_s": c4["B"] * c4["T"] / (ms * 1e-3), "layers": c4["layers"], "hidden": c4["hidden"],
+            "segments": c4["T"] // c4["segment"], "dtype": "bf16 activations, fp32 state"}
+
+
 def other_workloads(lib, device, hbm_peak):
     """Kernel-timed figures for the retrieval path (config 3) and a config-5 slab."""
     from rnn_with_grm_b200 import cabi
 
     out = {}
     out["full_occupancy_scan"] = full_occupancy_scan(lib, device, hbm_peak)
+    out["cfg4_model"] = config4_model(device)
+    torch.cuda.empty_cache()
     stream = torch.cuda.current_stream().cuda_stream
     # ---- config 3: one query per segment, causal top-4 over 32 archived 64x64 fp32 matrices ----
     rows, S, K, V, top_k = CFG3["B"] * CFG3["Hd"], CFG3["T"] // CFG3["segment"], CFG3["K"], CFG3["V"], CFG3["top_k"]

@@ -229,3 +229,30 @@ class StackedSegmentMemoryRunner:
         if self.language_model:
             y = F.linear(y, p["output_layer.weight"], p.get("output_layer.bias"))
         return y, torch.stack(finals, dim=0)
+
+
+def language_model_parameter_shapes(num_layers: int, hidden: int, key_dim: int, vocab: int, embed_dim: int,
+                                    route_dim: Optional[int] = None) -> Dict[str, Tuple[int, ...]]:
+    """Names and shapes of the parameters ``StackedSegmentMemoryRunner(language_model=True)`` reads, as
+    the reference's ``SegmentMemoryLanguageModel.state_dict()`` lays them out (grm/utils/train.py:192-225,
+    grm/core/multilayer_grm.py:105-160, grm/core/paper_grm.py:405-470).  Layer 0 takes the embedding,
+    the others the hidden state; the routing dimension defaults to the hidden size."""
+    route_dim = hidden if route_dim is None else route_dim
+    shapes: Dict[str, Tuple[int, ...]] = {"embedding.weight": (vocab, embed_dim)}
+    for i in range(num_layers):
+        d_in = embed_dim if i == 0 else hidden
+        base = f"grm_rnn.layers.{i}.grm."
+        shapes.update({
+            base + "memory_cell.key_proj.weight": (key_dim, d_in), base + "memory_cell.key_proj.bias": (key_dim,),
+            base + "memory_cell.value_proj.weight": (hidden, d_in), base + "memory_cell.value_proj.bias": (hidden,),
+            base + "memory_cell.query_proj.weight": (key_dim, d_in), base + "memory_cell.query_proj.bias": (key_dim,),
+            base + "gating_unit.query_projection.weight": (route_dim, d_in),
+            base + "gating_unit.key_projection.weight": (route_dim, d_in),
+            base + "aggregator.layer_norm.weight": (hidden,), base + "aggregator.layer_norm.bias": (hidden,),
+            base + "output_proj.weight": (hidden, hidden), base + "output_proj.bias": (hidden,),
+            f"grm_rnn.layers.{i}.layer_norm.weight": (hidden,), f"grm_rnn.layers.{i}.layer_norm.bias": (hidden,),
+        })
+    shapes.update({"grm_rnn.output_proj.weight": (hidden, hidden), "grm_rnn.output_proj.bias": (hidden,),
+                   "output_layer.weight": (vocab, hidden), "output_layer.bias": (vocab,)})
+    return shapes
+
