@@ -99,6 +99,7 @@ class SegmentMemoryRunner:
         self.input_size = params["memory_cell.key_proj.weight"].shape[1]
         self.route_dim = params["gating_unit.query_projection.weight"].shape[0]
         self.archive: Optional[SegmentMemoryArchive] = None
+        self.dense_retrieval = True    # False: always gather the selected matrices (retrieve_fuse kernel)
 
     def clear_memory(self) -> None:
         self.archive = None
@@ -120,18 +121,48 @@ class SegmentMemoryRunner:
                                                       1.0 / math.sqrt(self.route_dim), self.temperature, False)
         return gates, indices
 
+    def _dense_contrib(self, q_t: Tensor, gates: Tensor, indices: Tensor) -> Tensor:
+        """Gate-weighted retrieved state when many queries share few candidates.
+
+        With per-token routing every token of a segment picks among the same ``count`` archived
+        matrices, so applying the query to all of them is one small batched GEMM
+        (``[C, K] x [K, count*H]`` per batch row, cuBLAS) and the selection becomes a gather of
+        H-vectors: ``count*H*K`` reads per batch row instead of ``C*R*H*K`` (config 4: 15 candidates
+        against 512 tokens x 4 routes).  Same result as gather + apply-query up to summation order.
+        """
+        archive = self.archive
+        B, C, _ = q_t.shape
+        mem = archive.memories[:, : archive.count] if archive.head == 0 else archive.memories.index_select(
+            1, (torch.arange(archive.count, device=q_t.device) + archive.head) % archive.capacity)
+        mem = mem.reshape(B, archive.count * self.hidden, self.key_dim).to(q_t.dtype)
+        all_states = torch.matmul(q_t, mem.transpose(1, 2)).view(B, C, archive.count, self.hidden)
+        live = indices >= 0
+        picked = torch.gather(all_states, 2, indices.clamp_min(0).unsqueeze(-1).expand(-1, -1, -1, self.hidden))
+        weights = torch.where(live, gates, torch.zeros_like(gates)).to(picked.dtype)
+        return (picked * weights.unsqueeze(-1)).sum(dim=2)
+
     def _retrieve_and_fuse(self, x: Tensor, h_online: Tensor, gates: Tensor, indices: Tensor) -> Tensor:
         archive = self.archive
-        q_t = F.normalize(_linear(x, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6).float()
-        phys = archive.physical_indices(indices)
+        q_n = F.normalize(_linear(x, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6)
         ln_w = self.p.get("aggregator.layer_norm.weight") if self.use_layer_norm else None
         ln_b = self.p.get("aggregator.layer_norm.bias") if self.use_layer_norm else None
-        if self.mode == "residual" and self.use_layer_norm and "aggregator.output_projection.weight" not in self.p:
-            fused = torch.ops.grmx.retrieve_fuse(archive.memories, phys, gates, q_t, h_online.float(), ln_w, ln_b,
-                                                 self.eps, FUSE_RESIDUAL_LN)
-            return fused.to(h_online.dtype)
-        contrib = torch.ops.grmx.retrieve_fuse(archive.memories, phys, gates, q_t, None, None, None, self.eps,
-                                               FUSE_CONTRIB).to(h_online.dtype)
+        plain_residual = (self.mode == "residual" and self.use_layer_norm
+                          and "aggregator.output_projection.weight" not in self.p)
+        # queries x routes against candidates: the dense form reads every candidate once per batch row
+        dense = self.dense_retrieval and indices.shape[1] * indices.shape[2] >= 4 * archive.count
+        if dense:
+            contrib = self._dense_contrib(q_n, gates, indices).to(h_online.dtype)
+            if plain_residual:
+                return F.layer_norm(h_online + contrib, (self.hidden,), ln_w, ln_b, self.eps)
+        else:
+            q_t = q_n.float()
+            phys = archive.physical_indices(indices)
+            if plain_residual:
+                fused = torch.ops.grmx.retrieve_fuse(archive.memories, phys, gates, q_t, h_online.float(), ln_w, ln_b,
+                                                     self.eps, FUSE_RESIDUAL_LN)
+                return fused.to(h_online.dtype)
+            contrib = torch.ops.grmx.retrieve_fuse(archive.memories, phys, gates, q_t, None, None, None, self.eps,
+                                                   FUSE_CONTRIB).to(h_online.dtype)
         # aggregator.py:116-145
         if self.mode == "residual":
             fused = h_online + contrib
@@ -229,6 +260,38 @@ class StackedSegmentMemoryRunner:
         if self.language_model:
             y = F.linear(y, p["output_layer.weight"], p.get("output_layer.bias"))
         return y, torch.stack(finals, dim=0)
+
+
+class GraphedForward:
+    """A runner's forward pass for one input shape, captured once as a CUDA graph and replayed.
+
+    A forward pass is hundreds of small launches per layer (projections, normalisations, the kernels
+    of this package, one set per segment), and the segment loop is static for a given sequence length
+    when the archive is reset at the start of the call: the number of archived segments every
+    segment sees is known in advance.  Replaying the captured graph removes the host from the loop.
+    The inputs are copied into the buffer the graph was captured on; the outputs are the graph's own
+    buffers and are overwritten by the next call.
+    """
+
+    def __init__(self, runner, example_input: Tensor, warmup: int = 2):
+        if example_input.device.type != "cuda":
+            raise RuntimeError("GraphedForward needs a CUDA tensor")
+        self._input = example_input.clone()
+        side = torch.cuda.Stream(device=example_input.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):                       # first calls set kernel attributes, fill caches
+                runner.forward(self._input, reset_memory=True)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._output = runner.forward(self._input, reset_memory=True)
+
+    def __call__(self, x: Tensor):
+        self._input.copy_(x)
+        self._graph.replay()
+        return self._output
 
 
 def language_model_parameter_shapes(num_layers: int, hidden: int, key_dim: int, vocab: int, embed_dim: int,

@@ -45,6 +45,22 @@ def test_single_layer_model_matches_reference_forward(golden):
     assert aux2["num_segments"] == 8 and aux2["total_pushed"] == 8
 
 
+def test_graph_replay_of_the_forward_pass_matches_eager(golden):
+    from rnn_with_grm_b200.segment_memory import GraphedForward
+
+    g = golden("model_cfg1")
+    runner = _runner(g)
+    x = torch.from_numpy(g["x"]).to(DEV)
+    want_out, want_h, want_m, _ = runner.forward(x, reset_memory=True)
+    graphed = GraphedForward(runner, x)
+    for _ in range(2):                                  # a replay starts from an empty archive every time
+        out, h_final, memory, _ = graphed(x)
+        assert torch.equal(out, want_out) and torch.equal(h_final, want_h) and torch.equal(memory, want_m)
+    other = torch.rand_like(x)
+    out2 = graphed(other)[0].clone()
+    assert torch.equal(out2, runner.forward(other, reset_memory=True)[0])
+
+
 def test_archive_ring_keeps_fifo_order_after_eviction():
     archive = SegmentMemoryArchive(batch=2, capacity=3, hidden=4, key_dim=4, summary_dim=2, device=DEV)
     for i in range(5):
