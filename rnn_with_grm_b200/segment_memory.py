@@ -106,18 +106,10 @@ class SegmentMemoryRunner:
 
     # ---- pieces of one segment -------------------------------------------------------------
 
-    def _scan(self, x: Tensor, memory: Tensor) -> Tuple[Tensor, Tensor]:
-        # paper_grm.py:491-504
-        k = F.normalize(_linear(x, self.p, "memory_cell.key_proj"), p=2, dim=-1, eps=1e-6)
-        v = _linear(x, self.p, "memory_cell.value_proj")
-        q = F.normalize(_linear(x, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6)
-        return cuda_ops.cuda_chunk_update(k, v, q, memory, self.decay)
-
-    def _route(self, x: Tensor, summaries: Tensor) -> Tuple[Tensor, Tensor]:
+    def _route(self, route_q: Tensor, summaries: Tensor) -> Tuple[Tensor, Tensor]:
         # paper_grm.py:566-589: bias-free projections, scale 1/sqrt(route_dim), top-k, softmax
-        q_proj = F.linear(x.float(), self.p["gating_unit.query_projection.weight"].float())
-        k_proj = F.linear(summaries, self.p["gating_unit.key_projection.weight"].float())
-        gates, indices, _ = torch.ops.grmx.topk_route(q_proj, k_proj, None, self.top_k,
+        k_proj = F.linear(summaries, self._route_key_weight)
+        gates, indices, _ = torch.ops.grmx.topk_route(route_q, k_proj, None, self.top_k,
                                                       1.0 / math.sqrt(self.route_dim), self.temperature, False)
         return gates, indices
 
@@ -141,9 +133,9 @@ class SegmentMemoryRunner:
         weights = torch.where(live, gates, torch.zeros_like(gates)).to(picked.dtype)
         return (picked * weights.unsqueeze(-1)).sum(dim=2)
 
-    def _retrieve_and_fuse(self, x: Tensor, h_online: Tensor, gates: Tensor, indices: Tensor) -> Tensor:
+    def _retrieve_and_fuse(self, q_n: Tensor, h_online: Tensor, gates: Tensor, indices: Tensor) -> Tensor:
+        """``q_n``: the segment's normalised queries (paper_grm.py:301,312 recompute the same values)."""
         archive = self.archive
-        q_n = F.normalize(_linear(x, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6)
         ln_w = self.p.get("aggregator.layer_norm.weight") if self.use_layer_norm else None
         ln_b = self.p.get("aggregator.layer_norm.bias") if self.use_layer_norm else None
         plain_residual = (self.mode == "residual" and self.use_layer_norm
@@ -200,25 +192,56 @@ class SegmentMemoryRunner:
                                                                        device=x_seq.device, dtype=torch.float32)
         if x_seq.dtype == torch.float32:
             memory = memory.float()
-        outputs: List[Tensor] = []
+        # Everything that depends on the layer input alone is computed for the whole sequence at once
+        # (paper_grm.py:491-493, 522-523, 566-570 do it segment by segment): the three projections of
+        # the memory cell, the routing queries and the segment summaries.  Only the scan, the routing
+        # against the archive and the retrieval are sequential in the segments.
+        L = self.segment_length
+        bounds = [(s0, min(s0 + L, T)) for s0 in range(0, T, L)]
+
+        def per_segment(t: Tensor) -> List[Tensor]:
+            if T % L == 0 and T > 0:
+                stacked = t.reshape(B, T // L, L, t.shape[-1]).transpose(0, 1).contiguous()
+                return [stacked[i] for i in range(T // L)]
+            return [t[:, s0:s1].contiguous() for s0, s1 in bounds]
+
+        k_seg = per_segment(F.normalize(_linear(x_seq, self.p, "memory_cell.key_proj"), p=2, dim=-1, eps=1e-6))
+        v_seg = per_segment(_linear(x_seq, self.p, "memory_cell.value_proj"))
+        q_seg = per_segment(F.normalize(_linear(x_seq, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6))
+        x_f32 = x_seq.float()
+        if T % L == 0 and T > 0:
+            summaries = x_f32.reshape(B, T // L, L, -1).mean(dim=2)
+            summary_seg = [summaries[:, i] for i in range(T // L)]
+        else:
+            summary_seg = [x_f32[:, s0:s1].mean(dim=1) for s0, s1 in bounds]
+        routes_needed = archive.count > 0 or len(bounds) > 1
+        if routes_needed:
+            route_q_weight = self.p["gating_unit.query_projection.weight"].float()
+            self._route_key_weight = self.p["gating_unit.key_projection.weight"].float()
+            rq_seg = per_segment(F.linear(x_f32, route_q_weight))
+        del x_f32
+
+        hidden_seg: List[Tensor] = []
         routes = []
-        last_hidden = torch.zeros(B, self.hidden, device=x_seq.device, dtype=x_seq.dtype)
-        for start in range(0, T, self.segment_length):
-            x = x_seq[:, start:start + self.segment_length]
-            h_online, memory = self._scan(x, memory)
+        for i in range(len(bounds)):
+            h_online, memory = cuda_ops.cuda_chunk_update(k_seg[i], v_seg[i], q_seg[i], memory, self.decay)
             if archive.count > 0:                                   # paper_grm.py:620-621: no fusion otherwise
-                gates, indices = self._route(x, archive.ordered_summaries())
-                h = self._retrieve_and_fuse(x, h_online, gates, indices)
+                gates, indices = self._route(rq_seg[i], archive.ordered_summaries())
+                h = self._retrieve_and_fuse(q_seg[i], h_online, gates, indices)
                 if return_routes:
                     routes.append((gates, indices))
             else:
                 h = h_online
-            outputs.append(_linear(h, self.p, "output_proj"))
-            last_hidden = h[:, -1]
-            archive.push(memory, x.float().mean(dim=1))            # paper_grm.py:522-523, 721-725
+            hidden_seg.append(h)
+            archive.push(memory, summary_seg[i])                    # paper_grm.py:522-523, 721-725
             if self.init_mode == "independent":
                 memory = torch.zeros_like(memory)
-        out = torch.cat(outputs, dim=1) if outputs else x_seq.new_zeros(B, 0, self.p["output_proj.weight"].shape[0])
+        if hidden_seg:
+            last_hidden = hidden_seg[-1][:, -1]
+            out = _linear(torch.cat(hidden_seg, dim=1), self.p, "output_proj")
+        else:
+            last_hidden = torch.zeros(B, self.hidden, device=x_seq.device, dtype=x_seq.dtype)
+            out = x_seq.new_zeros(B, 0, self.p["output_proj.weight"].shape[0])
         aux = {"num_segments": archive.count, "total_pushed": archive.total_pushed}
         if return_routes:
             aux["routes"] = routes
