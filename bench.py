@@ -342,6 +342,30 @@ def full_occupancy_scan(lib, device, hbm_peak, launches=5):
             "bytes": nbytes, "row_tokens_per_s": rows * T / (ms * 1e-3)}
 
 
+def config2_backward(lib, device):
+    """Gradients of the config-2 scan (grad_keys, grad_values, grad_queries, grad_memory from grad_hidden
+    and grad_memory_out): three scans of the same tensor-core kernel, timed as one CUDA graph."""
+    from rnn_with_grm_b200 import cabi
+
+    rows, T, K, V, decay = CFG2["B"] * CFG2["Hd"], CFG2["T"], CFG2["K"], CFG2["V"], CFG2["decay"]
+    k, v, q = make_scan_inputs(rows, T, K, V, device, seed=21)
+    g = torch.Generator(device=device).manual_seed(22)
+    grad_h = torch.randn(rows, T, V, device=device, generator=g).to(torch.bfloat16)
+    grad_m = torch.randn(rows, V, K, device=device, generator=g)
+    m_in = torch.zeros(rows, V, K, device=device)
+    gk, gv, gq, gm = torch.empty_like(k), torch.empty_like(v), torch.empty_like(q), torch.empty_like(m_in)
+
+    def bwd(_, stream):
+        cabi.check(lib.grmx_chunk_scan_bwd(grad_h.data_ptr(), grad_m.data_ptr(), k.data_ptr(), v.data_ptr(), q.data_ptr(),
+                                           m_in.data_ptr(), gk.data_ptr(), gv.data_ptr(), gq.data_ptr(), gm.data_ptr(),
+                                           rows, T, K, V, decay, cabi.BF16, cabi.F32, cabi.PATH_AUTO, stream))
+
+    launches = 5
+    total_ms, _, _ = time_graph(bwd, launches, 3)
+    ms = total_ms / launches
+    return {"ms": ms, "tokens_per_s": CFG2["B"] * T / (ms * 1e-3)}
+
+
 def config4_model(device):
     """Config 4 end to end: the four-layer segment-memory language model (hidden 512, d_k 64, segment
     512, top-k 4, vocabulary 32768) over 8 x 8192 token ids, bf16 activations with fp32 state, run by
@@ -400,6 +424,7 @@ def other_workloads(lib, device, hbm_peak):
 
     out = {}
     out["full_occupancy_scan"] = full_occupancy_scan(lib, device, hbm_peak)
+    out["cfg2_backward"] = config2_backward(lib, device)
     out["cfg4_model"] = config4_model(device)
     torch.cuda.empty_cache()
     stream = torch.cuda.current_stream().cuda_stream
