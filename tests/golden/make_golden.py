@@ -3,7 +3,7 @@
 Run where a checkout of Sggggt/RNN_with_GRM is available (it is imported, not
 copied):
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference /root/reference
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py --reference <checkout of Sggggt/RNN_with_GRM>
 
 Every fixture is an ``.npz`` holding seeded inputs and the outputs of the
 reference's Python implementation on CPU in float32:
