@@ -277,6 +277,14 @@ int grmx_retrieve_fuse(const float* archive, const int64_t* indices, const float
 int grmx_device_error_word(uint32_t* out, void* stream);
 int grmx_device_error_reset(void* stream);
 
+/*
+ * Self-test of the bounded waits: launches one small CTA whose warps wait, with the kernels' own
+ * wait routine and a limit of `wait_limit` polls, on an mbarrier that nothing ever completes.
+ * The wait gives up, the CTA-wide abort flag stops the other warps, bit 1 of the device error
+ * word is set and the kernel returns: the context stays usable.  No counterpart in the reference.
+ */
+int grmx_selftest_bounded_wait(uint32_t wait_limit, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -75,6 +75,7 @@ SIGNATURES = {
     ),
     "grmx_device_error_word": (c_int, [POINTER(c_uint32), c_void_p]),
     "grmx_device_error_reset": (c_int, [c_void_p]),
+    "grmx_selftest_bounded_wait": (c_int, [c_uint32, c_void_p]),
 }
 
 _LIB: Optional[ctypes.CDLL] = None

@@ -4,6 +4,7 @@
 #include <cmath>
 
 #include "scan.cuh"
+#include "tc_ptx.cuh"
 
 namespace grmx {
 namespace {
@@ -216,6 +217,16 @@ int grmx_chunk_scan_bwd(const void* grad_hidden, const void* grad_memory_out,
   rc = grmx::run_scan(dv, io_dtype, state_dtype, path, s, who);
   if (rc != GRMX_OK) return rc;
   return grmx::run_scan(dk, io_dtype, state_dtype, path, s, who);
+}
+
+int grmx_selftest_bounded_wait(uint32_t wait_limit, void* stream) {
+  if (wait_limit == 0 || wait_limit > (1u << 24)) {
+    return grmx::fail(GRMX_ERR_ARG, "grmx_selftest_bounded_wait: wait_limit must be in [1, 2^24]");
+  }
+  if (!grmx::tc::device_is_sm100()) {
+    return grmx::fail(GRMX_ERR_UNSUPPORTED, "grmx_selftest_bounded_wait: needs an sm_100 device");
+  }
+  return grmx::tc::launch_bounded_wait_selftest(wait_limit, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -112,6 +112,31 @@ bool make_token_half_map(CUtensorMap* map, const void* base, int64_t B, int64_t 
   return encode_token_map(map, MapKey{base, B, T, D, 1});
 }
 
+namespace {
+
+// Four warps wait on a barrier that nothing completes.  The first to run out of polls raises the
+// abort flag, the others see it at their next check, and the CTA reports through the error word.
+__global__ void __launch_bounds__(128) bounded_wait_selftest_kernel(uint32_t limit, uint32_t* error_word) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  mbar_wait(&bar, 0, &abort_flag, limit);
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag && error_word != nullptr) atomicOr(error_word, kErrBoundedWait);
+}
+
+}  // namespace
+
+int launch_bounded_wait_selftest(uint32_t limit, cudaStream_t stream) {
+  bounded_wait_selftest_kernel<<<1, 128, 0, stream>>>(limit, device_error_word_ptr());
+  return check_launch("bounded_wait_selftest");
+}
+
 bool device_is_sm100() {
   static int cached[64] = {0};   // 0 unknown, 1 yes, 2 no
   int device = 0;

@@ -41,8 +41,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the
 // barrier did not flip within the limit or another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit = kWaitLimit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 63u && *abort_flag) return false;
   }
@@ -359,6 +360,8 @@ bool make_token_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, in
 // the same tensor as a store target: box = 32 features x 128 tokens x 1 row, 64-byte swizzle
 bool make_token_half_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, int64_t D);
 bool device_is_sm100();
+// one CTA that lets a bounded wait expire on purpose (see grmx_selftest_bounded_wait)
+int launch_bounded_wait_selftest(uint32_t limit, cudaStream_t stream);
 
 }  // namespace tc
 }  // namespace grmx

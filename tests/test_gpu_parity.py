@@ -464,3 +464,20 @@ def test_scratch_size_query():
     assert gx.chunk_scan_scratch_bytes(64, 256, 64, 64, torch.bfloat16, torch.float32) == 0      # too short
     assert gx.chunk_scan_scratch_bytes(64, 2048, 64, 64, torch.float32, torch.float32) == 0      # fp32 path
     assert gx.chunk_scan_scratch_bytes(64, 2048, 128, 128, torch.bfloat16, torch.float32) == 0
+
+
+def test_bounded_wait_gives_up_and_reports_without_losing_the_context():
+    """A wait that nothing will ever satisfy runs out of polls, the kernel returns, bit 1 of the
+    device error word is set, and the next launch on the same context works."""
+    lib = cabi.load()
+    assert cabi.device_error_word() == 0
+    cabi.check(lib.grmx_selftest_bounded_wait(1 << 12, cabi.current_stream()))
+    torch.cuda.synchronize()
+    assert cabi.device_error_word() == 2
+    cabi.check(lib.grmx_device_error_reset(cabi.current_stream()))
+    assert cabi.device_error_word() == 0
+    args, (want_h, _) = _tc_case(3, 2, 256, 0.97, False)
+    hidden, _ = gx.chunk_scan_fwd(*args, 0.97, cabi.PATH_TCGEN05)
+    close(hidden, want_h, LOWP_TOL)
+    assert cabi.device_error_word() == 0
+
