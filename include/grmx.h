@@ -270,6 +270,22 @@ int grmx_retrieve_fuse(const float* archive, const int64_t* indices, const float
                        int64_t Q, int64_t R, int64_t H, int64_t K, int mode, void* stream);
 
 /*
+ * The selection half of grmx_retrieve_fuse for callers that have already applied the query to every
+ * candidate: states [B,Q,S,H] (states[b,q,s,:] = M[b,s] q[b,q], e.g. one batched GEMM per batch row when
+ * all Q tokens of a segment choose among the same S archived matrices), indices int64 [B,Q,R] into S
+ * (-1 = empty route), gates float32 [B,Q,R].
+ *   GRMX_FUSE_CONTRIB:      out[b,q,:] = sum_r gates[r] * states[b,q,indices[r],:]
+ *   GRMX_FUSE_RESIDUAL_LN:  out[b,q,:] = LayerNorm(online[b,q,:] + that sum), ln_weight/ln_bias float32 [H]
+ *                           or NULL; a token without any live route returns online[b,q,:] unchanged
+ * states, online and out share `dtype` (GRMX_F32 or GRMX_BF16); sums and the normalisation are fp32.
+ * H <= 1024, R <= 32.  Follows grm/core/aggregator.py:104-105,116-118 (RetrievedStateFusion, "residual");
+ * the reference has no native counterpart.
+ */
+int grmx_select_fuse(const void* states, const int64_t* indices, const float* gates, const void* online,
+                     const float* ln_weight, const float* ln_bias, float ln_eps, void* out, int64_t B,
+                     int64_t Q, int64_t S, int64_t R, int64_t H, int dtype, int mode, void* stream);
+
+/*
  * Device error word: bit 0 = gather index out of range, bit 1 = a bounded
  * wait inside a kernel gave up.  grmx_device_error_word copies the word of
  * the current device to *out (synchronises that stream); reset clears it.

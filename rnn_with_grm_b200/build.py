@@ -41,6 +41,7 @@ CUDA_SOURCES = [
     "gather.cu",
     "topk_route.cu",
     "retrieve_fuse.cu",
+    "select_fuse.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -73,6 +73,10 @@ SIGNATURES = {
         c_int,
         [c_void_p] * 7 + [c_float, c_void_p] + [c_int64] * 6 + [c_int, c_void_p],
     ),
+    "grmx_select_fuse": (
+        c_int,
+        [c_void_p] * 6 + [c_float, c_void_p] + [c_int64] * 5 + [c_int, c_int, c_void_p],
+    ),
     "grmx_device_error_word": (c_int, [POINTER(c_uint32), c_void_p]),
     "grmx_device_error_reset": (c_int, [c_void_p]),
     "grmx_selftest_bounded_wait": (c_int, [c_uint32, c_void_p]),

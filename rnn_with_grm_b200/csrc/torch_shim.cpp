@@ -260,6 +260,49 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> topk_route_cuda(const at::Tensor&
   return {gates, idx, scores};
 }
 
+// states [B,Q,S,H] (fp32 or bf16), indices [B,Q,R], gates [B,Q,R] -> [B,Q,H] in the dtype of states
+at::Tensor select_fuse_cuda(const at::Tensor& states, const at::Tensor& indices, const at::Tensor& gates,
+                            const c10::optional<at::Tensor>& online, const c10::optional<at::Tensor>& ln_weight,
+                            const c10::optional<at::Tensor>& ln_bias, double ln_eps, int64_t mode) {
+  TORCH_CHECK(states.dim() == 4, "states must have shape [B, Q, S, H]");
+  TORCH_CHECK(indices.dim() == 3 && gates.dim() == 3, "indices and gates must have shape [B, Q, R]");
+  TORCH_CHECK(indices.sizes() == gates.sizes(), "indices and gates differ in shape");
+  TORCH_CHECK(states.size(0) == indices.size(0) && states.size(1) == indices.size(1), "batch/query dim mismatch");
+  require_cuda(states, "states");
+  require_cuda(indices, "indices");
+  require_cuda(gates, "gates");
+  TORCH_CHECK(states.scalar_type() == at::kFloat || states.scalar_type() == at::kBFloat16,
+              "states must be float32 or bfloat16");
+  c10::cuda::CUDAGuard guard(states.device());
+  auto st = states.contiguous();
+  auto idx = indices.toType(at::kLong).contiguous();
+  auto g = gates.to(at::kFloat).contiguous();
+  const int64_t B = st.size(0), Q = st.size(1), S = st.size(2), H = st.size(3), R = idx.size(2);
+  at::Tensor o_keep, w_keep, b_keep;
+  const void* o_ptr = nullptr;
+  if (online.has_value() && online->defined()) {
+    require_cuda(*online, "online");
+    o_keep = online->to(st.scalar_type()).contiguous();
+    TORCH_CHECK(o_keep.sizes() == at::IntArrayRef({B, Q, H}), "online has the wrong shape");
+    o_ptr = o_keep.data_ptr();
+  }
+  auto opt = [&](const c10::optional<at::Tensor>& t, const char* name, at::Tensor& keep) -> const float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    require_cuda(*t, name);
+    keep = t->to(at::kFloat).contiguous();
+    TORCH_CHECK(keep.numel() == H, name, " has the wrong shape");
+    return keep.data_ptr<float>();
+  };
+  const float* w_ptr = opt(ln_weight, "ln_weight", w_keep);
+  const float* b_ptr = opt(ln_bias, "ln_bias", b_keep);
+  at::Tensor out = at::empty({B, Q, H}, st.options());
+  check_status(grmx_select_fuse(st.data_ptr(), idx.data_ptr<int64_t>(), g.data_ptr<float>(), o_ptr, w_ptr, b_ptr,
+                                static_cast<float>(ln_eps), out.data_ptr(), B, Q, S, R, H,
+                                st.scalar_type() == at::kFloat ? GRMX_F32 : GRMX_BF16, static_cast<int>(mode),
+                                current_stream()));
+  return out;
+}
+
 at::Tensor retrieve_fuse_cuda(const at::Tensor& archive, const at::Tensor& indices,
                               const c10::optional<at::Tensor>& gates, const at::Tensor& queries,
                               const c10::optional<at::Tensor>& online,
@@ -325,12 +368,14 @@ TORCH_LIBRARY(grmx, m) {
   m.def("linear_scan(Tensor keys, Tensor values, Tensor queries, Tensor memory, float decay, float update_coeff, float hidden_scale, float memory_out_scale, bool reverse, bool first_step_no_decay, int path) -> (Tensor hidden, Tensor memory_out)");
   m.def("topk_route(Tensor queries, Tensor keys, Tensor? visible, int top_k, float scale, float temperature, bool return_scores) -> (Tensor gates, Tensor indices, Tensor scores)");
   m.def("retrieve_fuse(Tensor archive, Tensor indices, Tensor? gates, Tensor queries, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
+  m.def("select_fuse(Tensor states, Tensor indices, Tensor gates, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(grmx, CUDA, m) {
   m.impl("linear_scan", linear_scan_cuda);
   m.impl("topk_route", topk_route_cuda);
   m.impl("retrieve_fuse", retrieve_fuse_cuda);
+  m.impl("select_fuse", select_fuse_cuda);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

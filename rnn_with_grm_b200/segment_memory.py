@@ -113,25 +113,22 @@ class SegmentMemoryRunner:
                                                       1.0 / math.sqrt(self.route_dim), self.temperature, False)
         return gates, indices
 
-    def _dense_contrib(self, q_t: Tensor, gates: Tensor, indices: Tensor) -> Tensor:
-        """Gate-weighted retrieved state when many queries share few candidates.
+    def _dense_states(self, q_t: Tensor) -> Tensor:
+        """Every archived matrix of a batch row applied to every query of the segment: ``[B, C, count, H]``.
 
-        With per-token routing every token of a segment picks among the same ``count`` archived
+        With per-token routing all tokens of a segment pick among the same ``count`` archived
         matrices, so applying the query to all of them is one small batched GEMM
-        (``[C, K] x [K, count*H]`` per batch row, cuBLAS) and the selection becomes a gather of
-        H-vectors: ``count*H*K`` reads per batch row instead of ``C*R*H*K`` (config 4: 15 candidates
-        against 512 tokens x 4 routes).  Same result as gather + apply-query up to summation order.
+        (``[C, K] x [K, count*H]`` per batch row, cuBLAS) and the selection becomes a pick of
+        H-vectors (``torch.ops.grmx.select_fuse``): ``count*H*K`` reads per batch row instead of
+        ``C*R*H*K`` (config 4: 15 candidates against 512 tokens x 4 routes).  Same result as gather +
+        apply-query up to summation order.
         """
         archive = self.archive
         B, C, _ = q_t.shape
         mem = archive.memories[:, : archive.count] if archive.head == 0 else archive.memories.index_select(
             1, (torch.arange(archive.count, device=q_t.device) + archive.head) % archive.capacity)
         mem = mem.reshape(B, archive.count * self.hidden, self.key_dim).to(q_t.dtype)
-        all_states = torch.matmul(q_t, mem.transpose(1, 2)).view(B, C, archive.count, self.hidden)
-        live = indices >= 0
-        picked = torch.gather(all_states, 2, indices.clamp_min(0).unsqueeze(-1).expand(-1, -1, -1, self.hidden))
-        weights = torch.where(live, gates, torch.zeros_like(gates)).to(picked.dtype)
-        return (picked * weights.unsqueeze(-1)).sum(dim=2)
+        return torch.matmul(q_t, mem.transpose(1, 2)).view(B, C, archive.count, self.hidden)
 
     def _retrieve_and_fuse(self, q_n: Tensor, h_online: Tensor, gates: Tensor, indices: Tensor) -> Tensor:
         """``q_n``: the segment's normalised queries (paper_grm.py:301,312 recompute the same values)."""
@@ -143,9 +140,12 @@ class SegmentMemoryRunner:
         # queries x routes against candidates: the dense form reads every candidate once per batch row
         dense = self.dense_retrieval and indices.shape[1] * indices.shape[2] >= 4 * archive.count
         if dense:
-            contrib = self._dense_contrib(q_n, gates, indices).to(h_online.dtype)
+            states = self._dense_states(q_n)
             if plain_residual:
-                return F.layer_norm(h_online + contrib, (self.hidden,), ln_w, ln_b, self.eps)
+                return torch.ops.grmx.select_fuse(states, indices, gates, h_online.to(states.dtype), ln_w, ln_b,
+                                                  self.eps, FUSE_RESIDUAL_LN).to(h_online.dtype)
+            contrib = torch.ops.grmx.select_fuse(states, indices, gates, None, None, None, self.eps,
+                                                 FUSE_CONTRIB).to(h_online.dtype)
         else:
             q_t = q_n.float()
             phys = archive.physical_indices(indices)

@@ -141,3 +141,16 @@ def retrieve_fuse(archive, indices, gates, queries, online=None, ln_weight=None,
                                       cabi.ptr(online), cabi.ptr(ln_weight), cabi.ptr(ln_bias), float(eps),
                                       cabi.ptr(out), B, S, Q, R, H, K, mode, cabi.current_stream()))
     return out
+
+
+def select_fuse(states, indices, gates, online=None, ln_weight=None, ln_bias=None, eps=1e-5,
+                mode=cabi.FUSE_RESIDUAL_LN):
+    lib = cabi.load()
+    B, Q, S, H = states.shape
+    R = indices.shape[2]
+    out = torch.empty(B, Q, H, device=states.device, dtype=states.dtype)
+    cabi.check(lib.grmx_select_fuse(cabi.ptr(states), cabi.ptr(indices), cabi.ptr(gates), cabi.ptr(online),
+                                    cabi.ptr(ln_weight), cabi.ptr(ln_bias), float(eps), cabi.ptr(out), B, Q, S, R, H,
+                                    cabi.dtype_code(states.dtype), mode, cabi.current_stream()))
+    return out
+

@@ -317,6 +317,42 @@ def test_retrieve_fuse_equals_gather_then_apply(golden):
     assert torch.equal(fused, two_step)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, LOWP_TOL)])
+@pytest.mark.parametrize("H", [64, 512, 1000])
+def test_select_fuse_equals_the_fused_chain_on_dense_candidates(dtype, tol, H):
+    """Applying the query to every candidate first (what the caller does with one GEMM) and then
+    selecting must give what gather -> apply-query -> weighted sum -> LayerNorm gives."""
+    rng = np.random.default_rng(61 + H)
+    B, S, Q, R, K = 2, 5, 7, 3, 16
+    archive = rng.standard_normal((B, S, H, K)).astype(np.float32)
+    queries = rng.standard_normal((B, Q, K)).astype(np.float32)
+    idx = rng.integers(0, S, size=(B, Q, R))
+    idx[0, 1, 2] = -1                       # an empty route
+    idx[1, 3, :] = -1                       # a token with nothing to retrieve
+    gates = rng.random((B, Q, R)).astype(np.float32)
+    online = rng.standard_normal((B, Q, H)).astype(np.float32)
+    ln_w = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    ln_b = (0.1 * rng.standard_normal(H)).astype(np.float32)
+    states = np.einsum("bshk,bqk->bqsh", archive.astype(np.float64), queries.astype(np.float64))
+    t_states, t_online = dev(states.astype(np.float32), dtype), dev(online, dtype)
+    # oracle on the values the kernel actually sees
+    seen_states, seen_online = host(t_states).astype(np.float64), host(t_online).astype(np.float64)
+    live = idx >= 0
+    picked = np.take_along_axis(seen_states, np.clip(idx, 0, None)[..., None], axis=2)
+    contrib = (picked * np.where(live, gates, 0.0)[..., None]).sum(axis=2)
+    got = gx.select_fuse(t_states, dev(idx), dev(gates), mode=cabi.FUSE_CONTRIB)
+    close(got, contrib, tol)
+    x = seen_online + contrib
+    want = (x - x.mean(-1, keepdims=True)) / np.sqrt(x.var(-1, keepdims=True) + 1e-5) * ln_w + ln_b
+    want[1, 3] = seen_online[1, 3]          # no live route: the online state passes through
+    got = gx.select_fuse(t_states, dev(idx), dev(gates), t_online, dev(ln_w), dev(ln_b), 1e-5, cabi.FUSE_RESIDUAL_LN)
+    close(got, want, tol)
+    if dtype == torch.float32:              # and the same as the gather-based kernel on the archive itself
+        fused = gx.retrieve_fuse(dev(archive), dev(idx), dev(gates), dev(queries), dev(online), dev(ln_w), dev(ln_b))
+        close(got, host(fused), FP32_TOL)
+    assert cabi.device_error_word() == 0
+
+
 # --------------------------------------------------------------------------- chunk scan, tcgen05 path
 
 def _tc_case(seed, B, T, decay, zero_state):
