@@ -14,24 +14,55 @@ constexpr int kWarpsPerCta = 8;
 constexpr int kMaxPerLane = 32;   // register path covers H <= 1024
 constexpr int kMaxRoutes = 32;
 
-template <typename T>
-__device__ __forceinline__ float load_as_float(const T* p);
-template <>
-__device__ __forceinline__ float load_as_float<float>(const float* p) { return __ldg(p); }
-template <>
-__device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p) {
-  return __bfloat162float(*p);
+// VEC consecutive elements of a row as floats: one 16-byte load when VEC spans 16 bytes
+template <typename T, int VEC>
+__device__ __forceinline__ void load_piece(const T* p, float (&out)[VEC]) {
+  if constexpr (VEC == 1) {
+    if constexpr (sizeof(T) == 4) out[0] = __ldg(reinterpret_cast<const float*>(p));
+    else out[0] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
+  } else if constexpr (sizeof(T) == 4) {
+    static_assert(VEC == 4, "16 bytes of fp32");
+    const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+  } else {
+    static_assert(VEC == 8, "16 bytes of bf16");
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {            // bf16 -> fp32 is a shift
+      out[2 * j] = __uint_as_float(w[j] << 16);
+      out[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+  }
 }
-__device__ __forceinline__ void store_from_float(float* p, float v) { *p = v; }
-__device__ __forceinline__ void store_from_float(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-template <typename T>
+template <typename T, int VEC>
+__device__ __forceinline__ void store_piece(T* p, const float (&in)[VEC]) {
+  if constexpr (VEC == 1) {
+    if constexpr (sizeof(T) == 4) *reinterpret_cast<float*>(p) = in[0];
+    else *reinterpret_cast<__nv_bfloat16*>(p) = __float2bfloat16_rn(in[0]);
+  } else if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(in[0], in[1], in[2], in[3]);
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 pair = __floats2bfloat162_rn(in[2 * j], in[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// Lane l owns the pieces l, l + 32, ... of the row, VEC elements each.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ indices,
                    const float* __restrict__ gates, const T* __restrict__ online,
                    const float* __restrict__ ln_weight, const float* __restrict__ ln_bias, float ln_eps,
                    T* __restrict__ out, int64_t BQ, int S, int R, int H, int mode,
                    uint32_t* __restrict__ error_word) {
+  constexpr int kPieces = kMaxPerLane / VEC;
   const int lane = threadIdx.x & 31;
   const int64_t bq = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (bq >= BQ) return;   // whole warps leave together; no CTA barrier below
@@ -51,9 +82,20 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
   const T* cand = states + bq * (int64_t)S * H;
   const bool fuse = mode == GRMX_FUSE_RESIDUAL_LN;
 
-  float x[kMaxPerLane];
+  float x[kPieces][VEC];
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) x[i] = 0.0f;
+  for (int i = 0; i < kPieces; ++i) {
+    const int h = (lane + 32 * i) * VEC;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) x[i][j] = 0.0f;
+    if (fuse && h < H) load_piece<T, VEC>(online + bq * H + h, x[i]);
+  }
+  float contrib[kPieces][VEC];
+#pragma unroll
+  for (int i = 0; i < kPieces; ++i) {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) contrib[i][j] = 0.0f;
+  }
   for (int r = 0; r < R; ++r) {                             // gate-weighted sum in route order
     // every lane takes part in the shuffles, whatever part of the row it owns
     const int64_t idx = __shfl_sync(0xffffffffu, my_idx, r);
@@ -61,24 +103,31 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
     if (idx < 0) continue;                                   // the same for all lanes
     const T* row = cand + idx * H;
 #pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i) {
-      const int h = lane + 32 * i;
-      if (h < H) x[i] = fmaf(gate, load_as_float(row + h), x[i]);
+    for (int i = 0; i < kPieces; ++i) {
+      const int h = (lane + 32 * i) * VEC;
+      if (h < H) {
+        float m[VEC];
+        load_piece<T, VEC>(row + h, m);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) contrib[i][j] = fmaf(gate, m[j], contrib[i][j]);
+      }
     }
   }
   float sum = 0.0f;
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
-    const int h = lane + 32 * i;
-    if (fuse && h < H) x[i] += load_as_float(online + bq * H + h);
-    sum += x[i];
+  for (int i = 0; i < kPieces; ++i) {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      x[i][j] += contrib[i][j];       // online + contribution, as the reference adds them
+      sum += x[i][j];
+    }
   }
   if (!fuse || !live) {
     // the contribution alone, or (nothing archived for this token) the online state untouched
 #pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i) {
-      const int h = lane + 32 * i;
-      if (h < H) store_from_float(out + bq * H + h, x[i]);
+    for (int i = 0; i < kPieces; ++i) {
+      const int h = (lane + 32 * i) * VEC;
+      if (h < H) store_piece<T, VEC>(out + bq * H + h, x[i]);
     }
     return;
   }
@@ -87,26 +136,43 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
   const float mean = sum / (float)H;
   float sq = 0.0f;
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
-    const int h = lane + 32 * i;
+  for (int i = 0; i < kPieces; ++i) {
+    const int h = (lane + 32 * i) * VEC;
     if (h < H) {
-      const float d = x[i] - mean;
-      sq = fmaf(d, d, sq);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float d = x[i][j] - mean;
+        sq = fmaf(d, d, sq);
+      }
     }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
   const float rstd = rsqrtf(sq / (float)H + ln_eps);
 #pragma unroll
-  for (int i = 0; i < kMaxPerLane; ++i) {
-    const int h = lane + 32 * i;
+  for (int i = 0; i < kPieces; ++i) {
+    const int h = (lane + 32 * i) * VEC;
     if (h < H) {
-      float y = (x[i] - mean) * rstd;
-      if (ln_weight != nullptr) y *= ln_weight[h];
-      if (ln_bias != nullptr) y += ln_bias[h];
-      store_from_float(out + bq * H + h, y);
+      float y[VEC];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        y[j] = (x[i][j] - mean) * rstd;
+        if (ln_weight != nullptr) y[j] *= __ldg(ln_weight + h + j);
+        if (ln_bias != nullptr) y[j] += __ldg(ln_bias + h + j);
+      }
+      store_piece<T, VEC>(out + bq * H + h, y);
     }
   }
+}
+
+template <typename T, int VEC>
+void launch_select_fuse(const void* states, const int64_t* indices, const float* gates, const void* online,
+                        const float* ln_weight, const float* ln_bias, float ln_eps, void* out, int64_t BQ, int S,
+                        int R, int H, int mode, cudaStream_t s, uint32_t* err) {
+  const int64_t blocks = (BQ + kWarpsPerCta - 1) / kWarpsPerCta;
+  select_fuse_kernel<T, VEC><<<static_cast<unsigned>(blocks), kWarpsPerCta * 32, 0, s>>>(
+      static_cast<const T*>(states), indices, gates, static_cast<const T*>(online), ln_weight, ln_bias, ln_eps,
+      static_cast<T*>(out), BQ, S, R, H, mode, err);
 }
 
 }  // namespace
@@ -134,14 +200,17 @@ extern "C" int grmx_select_fuse(const void* states, const int64_t* indices, cons
   GRMX_REQUIRE(blocks <= 0x7fffffffLL, "%s: grid too large", who);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint32_t* err = device_error_word_ptr();
+  // 16-byte pieces when every row starts on a 16-byte boundary
+  const uintptr_t bases = reinterpret_cast<uintptr_t>(states) | reinterpret_cast<uintptr_t>(online) |
+                          reinterpret_cast<uintptr_t>(out);
+  const int per16 = dtype == GRMX_F32 ? 4 : 8;
+  const bool vec = H % per16 == 0 && (bases & 15u) == 0;
   if (dtype == GRMX_F32) {
-    select_fuse_kernel<float><<<static_cast<unsigned>(blocks), kWarpsPerCta * 32, 0, s>>>(
-        static_cast<const float*>(states), indices, gates, static_cast<const float*>(online), ln_weight, ln_bias,
-        ln_eps, static_cast<float*>(out), BQ, (int)S, (int)R, (int)H, mode, err);
+    if (vec) launch_select_fuse<float, 4>(states, indices, gates, online, ln_weight, ln_bias, ln_eps, out, BQ, (int)S, (int)R, (int)H, mode, s, err);
+    else launch_select_fuse<float, 1>(states, indices, gates, online, ln_weight, ln_bias, ln_eps, out, BQ, (int)S, (int)R, (int)H, mode, s, err);
   } else {
-    select_fuse_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), kWarpsPerCta * 32, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(states), indices, gates, static_cast<const __nv_bfloat16*>(online),
-        ln_weight, ln_bias, ln_eps, static_cast<__nv_bfloat16*>(out), BQ, (int)S, (int)R, (int)H, mode, err);
+    if (vec) launch_select_fuse<__nv_bfloat16, 8>(states, indices, gates, online, ln_weight, ln_bias, ln_eps, out, BQ, (int)S, (int)R, (int)H, mode, s, err);
+    else launch_select_fuse<__nv_bfloat16, 1>(states, indices, gates, online, ln_weight, ln_bias, ln_eps, out, BQ, (int)S, (int)R, (int)H, mode, s, err);
   }
   return check_launch("select_fuse");
 }

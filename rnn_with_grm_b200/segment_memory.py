@@ -100,6 +100,12 @@ class SegmentMemoryRunner:
         self.route_dim = params["gating_unit.query_projection.weight"].shape[0]
         self.archive: Optional[SegmentMemoryArchive] = None
         self.dense_retrieval = True    # False: always gather the selected matrices (retrieve_fuse kernel)
+        # Per-token routing scores every token against at most ``capacity`` summaries.  Folded, the
+        # query projection is applied to those few projected keys (``[S, route_dim] x [route_dim, D]``)
+        # and the tokens are scored unprojected: the ``[B*T, D] x [D, route_dim]`` fp32 GEMM disappears.
+        # The scores are the same sums associated differently, equal to fp32 rounding.
+        self.fold_routing_projection = True
+        self._route_query_weight: Optional[Tensor] = None
 
     def clear_memory(self) -> None:
         self.archive = None
@@ -107,8 +113,12 @@ class SegmentMemoryRunner:
     # ---- pieces of one segment -------------------------------------------------------------
 
     def _route(self, route_q: Tensor, summaries: Tensor) -> Tuple[Tensor, Tensor]:
+        """``route_q``: the projected routing queries, or (folded form) the fp32 layer input itself."""
         # paper_grm.py:566-589: bias-free projections, scale 1/sqrt(route_dim), top-k, softmax
         k_proj = F.linear(summaries, self._route_key_weight)
+        if self._route_query_weight is not None:
+            # (x Wq^T) . (s Wk^T) == x . ((s Wk^T) Wq): project the few keys back instead of every token forward
+            k_proj = torch.matmul(k_proj, self._route_query_weight)
         gates, indices, _ = torch.ops.grmx.topk_route(route_q, k_proj, None, self.top_k,
                                                       1.0 / math.sqrt(self.route_dim), self.temperature, False)
         return gates, indices
@@ -218,7 +228,12 @@ class SegmentMemoryRunner:
         if routes_needed:
             route_q_weight = self.p["gating_unit.query_projection.weight"].float()
             self._route_key_weight = self.p["gating_unit.key_projection.weight"].float()
-            rq_seg = per_segment(F.linear(x_f32, route_q_weight))
+            if self.fold_routing_projection and self.input_size <= 2 * self.route_dim:
+                self._route_query_weight = route_q_weight
+                rq_seg = per_segment(x_f32)
+            else:
+                self._route_query_weight = None
+                rq_seg = per_segment(F.linear(x_f32, route_q_weight))
         del x_f32
 
         hidden_seg: List[Tensor] = []

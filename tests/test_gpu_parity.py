@@ -245,6 +245,27 @@ def test_topk_route_bit_exact_against_c_oracle():
     assert torch.equal(idx2, idx) and torch.equal(gates2, gates)
 
 
+@pytest.mark.parametrize("B,Q,S,D,top_k", [(2, 64, 1, 64, 4), (3, 70, 5, 36, 4), (2, 512, 15, 512, 4), (1, 97, 16, 128, 16),
+                                           (2, 130, 9, 4, 2), (1, 64, 16, 1024, 3), (1, 64, 16, 1028, 3)])
+def test_topk_route_with_few_keys_and_many_queries_bit_exact(B, Q, S, D, top_k):
+    """Per-token routing shapes take the kernel that stages the keys in shared memory; its scores,
+    indices and gates must be those of the C oracle bit for bit, ragged last CTA included."""
+    rng = np.random.default_rng(47 + Q + S)
+    qv = rng.standard_normal((B, Q, D)).astype(np.float32)
+    kv = rng.standard_normal((B, S, D)).astype(np.float32)
+    kv[:, S // 2] = kv[:, 0]                                   # equal scores: the lower index wins
+    visible = rng.integers(0, S + 2, size=Q).astype(np.int32)
+    scale = 1.0 / np.sqrt(D)
+    want_scores = oracle.c_route_scores(qv, kv, scale)
+    for vis in (None, visible):
+        want_idx, want_gates = oracle.c_topk_select(want_scores, top_k, 0.9, vis)
+        idx, gates, scores = gx.topk_route(dev(qv), dev(kv), top_k, scale, 0.9, None if vis is None else dev(vis))
+        assert np.array_equal(host(scores), want_scores)
+        assert np.array_equal(idx.cpu().numpy(), want_idx)
+        close(gates, want_gates, FP32_TOL)
+    assert cabi.device_error_word() == 0
+
+
 def test_topk_matches_reference_retriever_fixtures(golden):
     for name in ("topk", "identity"):
         g = golden(f"retriever_{name}")
