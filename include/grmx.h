@@ -286,6 +286,17 @@ int grmx_select_fuse(const void* states, const int64_t* indices, const float* ga
                      int64_t Q, int64_t S, int64_t R, int64_t H, int dtype, int mode, void* stream);
 
 /*
+ * archive[b, slot, :] = memory[b, :] and, when archive_bf16 is not NULL, the same values rounded to
+ * bf16 into archive_bf16[b, slot, :].  memory float32 [B,row_elems] (row_elems = H*K), archive float32
+ * [B,S,row_elems], archive_bf16 bf16 [B,S,row_elems] or NULL.  One pass over the state: the bf16 ring is
+ * what a caller multiplies with when it applies the queries of a segment to all archived matrices at once.
+ * Follows the append of the reference's _BatchMemoryArchive (grm/core/paper_grm.py:31-44, 721-725) on a
+ * preallocated device ring; the reference has no native counterpart.
+ */
+int grmx_archive_push(const float* memory, float* archive, void* archive_bf16, int64_t B, int64_t S,
+                      int64_t slot, int64_t row_elems, void* stream);
+
+/*
  * Device error word: bit 0 = gather index out of range, bit 1 = a bounded
  * wait inside a kernel gave up.  grmx_device_error_word copies the word of
  * the current device to *out (synchronises that stream); reset clears it.

@@ -42,6 +42,7 @@ CUDA_SOURCES = [
     "topk_route.cu",
     "retrieve_fuse.cu",
     "select_fuse.cu",
+    "archive_push.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

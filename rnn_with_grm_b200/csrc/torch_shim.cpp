@@ -303,6 +303,25 @@ at::Tensor select_fuse_cuda(const at::Tensor& states, const at::Tensor& indices,
   return out;
 }
 
+void archive_push_cuda(const at::Tensor& memory, at::Tensor archive, c10::optional<at::Tensor> shadow, int64_t slot) {
+  TORCH_CHECK(archive.dim() == 4 && memory.dim() == 3, "memory [B, H, K] goes into archive [B, S, H, K]");
+  TORCH_CHECK(memory.is_cuda() && archive.is_cuda(), "archive_push needs CUDA tensors");
+  TORCH_CHECK(memory.scalar_type() == at::kFloat && archive.scalar_type() == at::kFloat, "memory and archive are float32");
+  TORCH_CHECK(archive.is_contiguous(), "archive must be contiguous: it is written in place");
+  const int64_t B = archive.size(0), S = archive.size(1), H = archive.size(2), K = archive.size(3);
+  TORCH_CHECK(memory.size(0) == B && memory.size(1) == H && memory.size(2) == K, "memory does not match the archive");
+  void* shadow_ptr = nullptr;
+  if (shadow.has_value() && shadow->defined()) {
+    TORCH_CHECK(shadow->scalar_type() == at::kBFloat16 && shadow->is_contiguous() && shadow->sizes() == archive.sizes() &&
+                    shadow->is_cuda(), "the bf16 ring must be a contiguous bfloat16 CUDA tensor shaped like the archive");
+    shadow_ptr = shadow->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(archive.device());
+  auto mem = memory.contiguous();
+  check_status(grmx_archive_push(mem.data_ptr<float>(), archive.data_ptr<float>(), shadow_ptr, B, S, slot, H * K,
+                                 current_stream()));
+}
+
 at::Tensor retrieve_fuse_cuda(const at::Tensor& archive, const at::Tensor& indices,
                               const c10::optional<at::Tensor>& gates, const at::Tensor& queries,
                               const c10::optional<at::Tensor>& online,
@@ -368,6 +387,7 @@ TORCH_LIBRARY(grmx, m) {
   m.def("linear_scan(Tensor keys, Tensor values, Tensor queries, Tensor memory, float decay, float update_coeff, float hidden_scale, float memory_out_scale, bool reverse, bool first_step_no_decay, int path) -> (Tensor hidden, Tensor memory_out)");
   m.def("topk_route(Tensor queries, Tensor keys, Tensor? visible, int top_k, float scale, float temperature, bool return_scores) -> (Tensor gates, Tensor indices, Tensor scores)");
   m.def("retrieve_fuse(Tensor archive, Tensor indices, Tensor? gates, Tensor queries, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
+  m.def("archive_push(Tensor memory, Tensor(a!) archive, Tensor(b!)? shadow, int slot) -> ()");
   m.def("select_fuse(Tensor states, Tensor indices, Tensor gates, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
 }
 
@@ -376,6 +396,7 @@ TORCH_LIBRARY_IMPL(grmx, CUDA, m) {
   m.impl("topk_route", topk_route_cuda);
   m.impl("retrieve_fuse", retrieve_fuse_cuda);
   m.impl("select_fuse", select_fuse_cuda);
+  m.impl("archive_push", archive_push_cuda);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

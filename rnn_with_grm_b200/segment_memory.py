@@ -43,14 +43,51 @@ class SegmentMemoryArchive:
         self.capacity = int(capacity)
         self.memories = torch.empty(batch, self.capacity, hidden, key_dim, device=device, dtype=torch.float32)
         self.summaries = torch.empty(batch, self.capacity, summary_dim, device=device, dtype=torch.float32)
+        # the summaries as the router scores them (projected once, when the segment is archived)
+        self.route_keys: Optional[Tensor] = None
+        # bf16 copy of ``memories`` for retrieval with bf16 activations, written by the same kernel
+        self.memories_bf16: Optional[Tensor] = None
         self.count = 0      # segments held
         self.head = 0       # physical slot of the oldest segment
         self.total_pushed = 0
 
-    def push(self, memory: Tensor, summary: Tensor) -> None:
+    def _route_key_buffer(self, dim: int) -> Tensor:
+        if self.route_keys is None or self.route_keys.shape[-1] != dim:
+            if self.count > 0:
+                raise RuntimeError("route keys must be pushed with every segment or with none")
+            self.route_keys = torch.empty(self.summaries.shape[0], self.capacity, dim,
+                                          device=self.summaries.device, dtype=torch.float32)
+        return self.route_keys
+
+    def write_ahead(self, summaries: Tensor, route_keys: Tensor) -> bool:
+        """Store the summaries and routing keys ``[B, n, D]`` of the next ``n`` pushes with one copy
+        each.  Only when those pushes evict nothing and their slots do not wrap: the slots are then
+        free and stay invisible (beyond ``count``) until their push.  Returns whether it was done; if
+        so, the pushes pass ``summary=None``."""
+        n = summaries.shape[1]
+        first = self.head + self.count
+        if n == 0 or first + n > self.capacity:
+            return False
+        self.summaries[:, first:first + n].copy_(summaries)
+        self._route_key_buffer(route_keys.shape[-1])[:, first:first + n].copy_(route_keys)
+        return True
+
+    def keep_bf16_copy(self) -> None:
+        if self.memories_bf16 is None:
+            self.memories_bf16 = self.memories.to(torch.bfloat16)
+
+    def push(self, memory: Tensor, summary: Optional[Tensor], route_key: Optional[Tensor] = None) -> None:
         slot = (self.head + self.count) % self.capacity
-        self.memories[:, slot].copy_(memory)
-        self.summaries[:, slot].copy_(summary)
+        if memory.is_cuda and memory.dtype == torch.float32:
+            torch.ops.grmx.archive_push(memory, self.memories, self.memories_bf16, slot)
+        else:
+            self.memories[:, slot].copy_(memory)
+            if self.memories_bf16 is not None:
+                self.memories_bf16[:, slot].copy_(memory)
+        if summary is not None:
+            self.summaries[:, slot].copy_(summary)
+        if summary is not None and route_key is not None:
+            self._route_key_buffer(route_key.shape[-1])[:, slot].copy_(route_key)
         if self.count < self.capacity:
             self.count += 1
         else:
@@ -63,6 +100,13 @@ class SegmentMemoryArchive:
             return self.summaries[:, : self.count]
         order = (torch.arange(self.count, device=self.summaries.device) + self.head) % self.capacity
         return self.summaries.index_select(1, order)
+
+    def ordered_route_keys(self) -> Tensor:
+        """``[B, count, D_route]`` in FIFO order."""
+        if self.head == 0:
+            return self.route_keys[:, : self.count]
+        order = (torch.arange(self.count, device=self.route_keys.device) + self.head) % self.capacity
+        return self.route_keys.index_select(1, order)
 
     def physical_indices(self, indices: Tensor) -> Tensor:
         """FIFO positions -> slots of ``self.memories`` (empty slots, -1, stay -1)."""
@@ -104,6 +148,7 @@ class SegmentMemoryRunner:
         # query projection is applied to those few projected keys (``[S, route_dim] x [route_dim, D]``)
         # and the tokens are scored unprojected: the ``[B*T, D] x [D, route_dim]`` fp32 GEMM disappears.
         # The scores are the same sums associated differently, equal to fp32 rounding.
+        # Set it before the first call (the archive keeps the keys in the form they were pushed in).
         self.fold_routing_projection = True
         self._route_query_weight: Optional[Tensor] = None
 
@@ -112,14 +157,20 @@ class SegmentMemoryRunner:
 
     # ---- pieces of one segment -------------------------------------------------------------
 
-    def _route(self, route_q: Tensor, summaries: Tensor) -> Tuple[Tensor, Tensor]:
-        """``route_q``: the projected routing queries, or (folded form) the fp32 layer input itself."""
-        # paper_grm.py:566-589: bias-free projections, scale 1/sqrt(route_dim), top-k, softmax
-        k_proj = F.linear(summaries, self._route_key_weight)
+    def _route_keys(self, summaries: Tensor) -> Tensor:
+        """Segment summaries ``[B, n, D]`` as the router scores them (paper_grm.py:566-570: bias-free
+        key projection).  In the folded form the query projection is applied here as well:
+        ``(x Wq^T) . (s Wk^T) == x . ((s Wk^T) Wq)``, so the few keys are projected back instead of
+        every token forward."""
+        keys = F.linear(summaries, self._route_key_weight)
         if self._route_query_weight is not None:
-            # (x Wq^T) . (s Wk^T) == x . ((s Wk^T) Wq): project the few keys back instead of every token forward
-            k_proj = torch.matmul(k_proj, self._route_query_weight)
-        gates, indices, _ = torch.ops.grmx.topk_route(route_q, k_proj, None, self.top_k,
+            keys = torch.matmul(keys, self._route_query_weight)
+        return keys
+
+    def _route(self, route_q: Tensor, keys: Tensor) -> Tuple[Tensor, Tensor]:
+        """``route_q``: the projected routing queries, or (folded form) the fp32 layer input itself."""
+        # paper_grm.py:571-589: scale 1/sqrt(route_dim), top-k, softmax over the selected scores
+        gates, indices, _ = torch.ops.grmx.topk_route(route_q, keys, None, self.top_k,
                                                       1.0 / math.sqrt(self.route_dim), self.temperature, False)
         return gates, indices
 
@@ -135,7 +186,9 @@ class SegmentMemoryRunner:
         """
         archive = self.archive
         B, C, _ = q_t.shape
-        mem = archive.memories[:, : archive.count] if archive.head == 0 else archive.memories.index_select(
+        ring = archive.memories_bf16 if q_t.dtype == torch.bfloat16 and archive.memories_bf16 is not None \
+            else archive.memories
+        mem = ring[:, : archive.count] if archive.head == 0 else ring.index_select(
             1, (torch.arange(archive.count, device=q_t.device) + archive.head) % archive.capacity)
         mem = mem.reshape(B, archive.count * self.hidden, self.key_dim).to(q_t.dtype)
         return torch.matmul(q_t, mem.transpose(1, 2)).view(B, C, archive.count, self.hidden)
@@ -197,6 +250,8 @@ class SegmentMemoryRunner:
             self.archive = SegmentMemoryArchive(B, self.capacity, self.hidden, self.key_dim, self.input_size,
                                                 x_seq.device)
         archive = self.archive
+        if x_seq.dtype == torch.bfloat16 and self.dense_retrieval:
+            archive.keep_bf16_copy()
         # the carried state stays fp32 whatever the activations are
         memory = c_init.float() if c_init is not None else torch.zeros(B, self.hidden, self.key_dim,
                                                                        device=x_seq.device, dtype=torch.float32)
@@ -221,19 +276,25 @@ class SegmentMemoryRunner:
         x_f32 = x_seq.float()
         if T % L == 0 and T > 0:
             summaries = x_f32.reshape(B, T // L, L, -1).mean(dim=2)
-            summary_seg = [summaries[:, i] for i in range(T // L)]
+        elif bounds:
+            summaries = torch.stack([x_f32[:, s0:s1].mean(dim=1) for s0, s1 in bounds], dim=1)
         else:
-            summary_seg = [x_f32[:, s0:s1].mean(dim=1) for s0, s1 in bounds]
-        routes_needed = archive.count > 0 or len(bounds) > 1
-        if routes_needed:
-            route_q_weight = self.p["gating_unit.query_projection.weight"].float()
-            self._route_key_weight = self.p["gating_unit.key_projection.weight"].float()
-            if self.fold_routing_projection and self.input_size <= 2 * self.route_dim:
-                self._route_query_weight = route_q_weight
-                rq_seg = per_segment(x_f32)
-            else:
-                self._route_query_weight = None
-                rq_seg = per_segment(F.linear(x_f32, route_q_weight))
+            summaries = x_f32.new_zeros(B, 0, x_f32.shape[-1])
+        summary_seg = [summaries[:, i] for i in range(len(bounds))]
+        # The routing keys of this call's segments are projected once, here, and archived with them
+        # (the reference projects the archived summaries again in every segment, paper_grm.py:566-570;
+        # the weights do not change during a forward pass).  The queries are only needed if some
+        # segment will see a non-empty archive.
+        route_q_weight = self.p["gating_unit.query_projection.weight"].float()
+        self._route_key_weight = self.p["gating_unit.key_projection.weight"].float()
+        fold = self.fold_routing_projection and self.input_size <= 2 * self.route_dim
+        self._route_query_weight = route_q_weight if fold else None
+        route_key_all = self._route_keys(summaries)
+        route_key_seg = [route_key_all[:, i] for i in range(len(bounds))]
+        if archive.write_ahead(summaries, route_key_all):
+            summary_seg = [None] * len(bounds)
+        if archive.count > 0 or len(bounds) > 1:
+            rq_seg = per_segment(x_f32 if fold else F.linear(x_f32, route_q_weight))
         del x_f32
 
         hidden_seg: List[Tensor] = []
@@ -241,14 +302,14 @@ class SegmentMemoryRunner:
         for i in range(len(bounds)):
             h_online, memory = cuda_ops.cuda_chunk_update(k_seg[i], v_seg[i], q_seg[i], memory, self.decay)
             if archive.count > 0:                                   # paper_grm.py:620-621: no fusion otherwise
-                gates, indices = self._route(rq_seg[i], archive.ordered_summaries())
+                gates, indices = self._route(rq_seg[i], archive.ordered_route_keys())
                 h = self._retrieve_and_fuse(q_seg[i], h_online, gates, indices)
                 if return_routes:
                     routes.append((gates, indices))
             else:
                 h = h_online
             hidden_seg.append(h)
-            archive.push(memory, summary_seg[i])                    # paper_grm.py:522-523, 721-725
+            archive.push(memory, summary_seg[i], route_key_seg[i])  # paper_grm.py:522-523, 721-725
             if self.init_mode == "independent":
                 memory = torch.zeros_like(memory)
         if hidden_seg:

@@ -154,3 +154,10 @@ def select_fuse(states, indices, gates, online=None, ln_weight=None, ln_bias=Non
                                     cabi.dtype_code(states.dtype), mode, cabi.current_stream()))
     return out
 
+
+
+def archive_push(memory, archive, shadow, slot):
+    lib = cabi.load()
+    B, S, H, K = archive.shape
+    cabi.check(lib.grmx_archive_push(cabi.ptr(memory), cabi.ptr(archive), cabi.ptr(shadow), B, S, slot, H * K,
+                                     cabi.current_stream()))

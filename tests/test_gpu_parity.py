@@ -227,6 +227,25 @@ def test_gather_empty_slots_and_bad_indices():
     assert gx.batched_gather(mem[:, :0], dev(np.zeros((2, 0), dtype=np.int64))).shape == (2, 0, 4, 4)
 
 
+@pytest.mark.parametrize("H,K", [(64, 64), (5, 3), (512, 64)])
+def test_archive_push_writes_the_slot_and_its_bf16_copy(H, K):
+    rng = np.random.default_rng(29 + H)
+    B, S = 3, 4
+    archive = dev(rng.standard_normal((B, S, H, K)).astype(np.float32))
+    shadow = archive.to(torch.bfloat16)
+    before, before_shadow = archive.clone(), shadow.clone()
+    memory = dev(rng.standard_normal((B, H, K)).astype(np.float32))
+    gx.archive_push(memory, archive, shadow, 2)
+    gx.archive_push(memory, archive, None, 0)                  # without the bf16 ring
+    before[:, 2] = memory
+    before[:, 0] = memory
+    before_shadow[:, 2] = memory.to(torch.bfloat16)
+    assert torch.equal(archive, before) and torch.equal(shadow, before_shadow)
+    lib = cabi.load()
+    rc = lib.grmx_archive_push(cabi.ptr(memory), cabi.ptr(archive), None, B, S, S, H * K, cabi.current_stream())
+    assert rc == 1 and b"slot" in lib.grmx_last_error()        # GRMX_ERR_ARG, nothing launched
+
+
 # --------------------------------------------------------------------------- routing
 
 def test_topk_route_bit_exact_against_c_oracle():
