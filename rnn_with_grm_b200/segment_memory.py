@@ -151,9 +151,30 @@ class SegmentMemoryRunner:
         # Set it before the first call (the archive keeps the keys in the form they were pushed in).
         self.fold_routing_projection = True
         self._route_query_weight: Optional[Tensor] = None
+        self._fp32_cache: Dict[str, Tuple[Tensor, Tensor, int]] = {}
+        self._visible_cache: Dict[Tuple[int, int, str], Tensor] = {}
 
     def clear_memory(self) -> None:
         self.archive = None
+
+    def _fp32_param(self, name: str) -> Optional[Tensor]:
+        """The parameter as the kernels read it (fp32), converted once per parameter tensor."""
+        t = self.p.get(name)
+        if t is None or t.dtype == torch.float32:
+            return t
+        cached = self._fp32_cache.get(name)
+        if cached is None or cached[0] is not t or cached[2] != t._version:
+            cached = (t, t.float(), t._version)
+            self._fp32_cache[name] = cached
+        return cached[1]
+
+    def _visible_counts(self, queries: int, count: int, device) -> Tensor:
+        key = (queries, count, str(device))
+        t = self._visible_cache.get(key)
+        if t is None:
+            t = torch.full((queries,), count, device=device, dtype=torch.int32)
+            self._visible_cache[key] = t
+        return t
 
     # ---- pieces of one segment -------------------------------------------------------------
 
@@ -167,10 +188,11 @@ class SegmentMemoryRunner:
             keys = torch.matmul(keys, self._route_query_weight)
         return keys
 
-    def _route(self, route_q: Tensor, keys: Tensor) -> Tuple[Tensor, Tensor]:
-        """``route_q``: the projected routing queries, or (folded form) the fp32 layer input itself."""
+    def _route(self, route_q: Tensor, keys: Tensor, visible: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+        """``route_q``: the projected routing queries, or (folded form) the fp32 layer input itself.
+        ``visible``: per query, how many of the leading keys it may choose from (all if None)."""
         # paper_grm.py:571-589: scale 1/sqrt(route_dim), top-k, softmax over the selected scores
-        gates, indices, _ = torch.ops.grmx.topk_route(route_q, keys, None, self.top_k,
+        gates, indices, _ = torch.ops.grmx.topk_route(route_q, keys, visible, self.top_k,
                                                       1.0 / math.sqrt(self.route_dim), self.temperature, False)
         return gates, indices
 
@@ -196,8 +218,8 @@ class SegmentMemoryRunner:
     def _retrieve_and_fuse(self, q_n: Tensor, h_online: Tensor, gates: Tensor, indices: Tensor) -> Tensor:
         """``q_n``: the segment's normalised queries (paper_grm.py:301,312 recompute the same values)."""
         archive = self.archive
-        ln_w = self.p.get("aggregator.layer_norm.weight") if self.use_layer_norm else None
-        ln_b = self.p.get("aggregator.layer_norm.bias") if self.use_layer_norm else None
+        ln_w = self._fp32_param("aggregator.layer_norm.weight") if self.use_layer_norm else None
+        ln_b = self._fp32_param("aggregator.layer_norm.bias") if self.use_layer_norm else None
         plain_residual = (self.mode == "residual" and self.use_layer_norm
                           and "aggregator.output_projection.weight" not in self.p)
         # queries x routes against candidates: the dense form reads every candidate once per batch row
@@ -285,8 +307,8 @@ class SegmentMemoryRunner:
         # (the reference projects the archived summaries again in every segment, paper_grm.py:566-570;
         # the weights do not change during a forward pass).  The queries are only needed if some
         # segment will see a non-empty archive.
-        route_q_weight = self.p["gating_unit.query_projection.weight"].float()
-        self._route_key_weight = self.p["gating_unit.key_projection.weight"].float()
+        route_q_weight = self._fp32_param("gating_unit.query_projection.weight")
+        self._route_key_weight = self._fp32_param("gating_unit.key_projection.weight")
         fold = self.fold_routing_projection and self.input_size <= 2 * self.route_dim
         self._route_query_weight = route_q_weight if fold else None
         route_key_all = self._route_keys(summaries)
@@ -302,7 +324,13 @@ class SegmentMemoryRunner:
         for i in range(len(bounds)):
             h_online, memory = cuda_ops.cuda_chunk_update(k_seg[i], v_seg[i], q_seg[i], memory, self.decay)
             if archive.count > 0:                                   # paper_grm.py:620-621: no fusion otherwise
-                gates, indices = self._route(rq_seg[i], archive.ordered_route_keys())
+                if archive.head == 0 and archive.capacity <= 16:
+                    # the whole ring with the number of archived segments as the visible count: the
+                    # same selection as over ring[:, :count], without copying that slice
+                    gates, indices = self._route(rq_seg[i], archive.route_keys,
+                                                 self._visible_counts(rq_seg[i].shape[1], archive.count, x_seq.device))
+                else:
+                    gates, indices = self._route(rq_seg[i], archive.ordered_route_keys())
                 h = self._retrieve_and_fuse(q_seg[i], h_online, gates, indices)
                 if return_routes:
                     routes.append((gates, indices))
