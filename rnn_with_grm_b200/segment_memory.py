@@ -263,45 +263,67 @@ class SegmentMemoryRunner:
     def forward(self, x_seq: Tensor, c_init: Optional[Tensor] = None, reset_memory: bool = False,
                 return_routes: bool = False):
         """``x_seq [B, T, D]`` -> ``(outputs [B, T, out], h_final [B, H], memory_final [B, H, K], aux)``."""
-        if x_seq.device.type != "cuda":
-            raise RuntimeError("SegmentMemoryRunner needs CUDA tensors; this engine has no CPU path")
         B, T, _ = x_seq.shape
+        L = self.segment_length
+        if T > 0 and T % L == 0:
+            x_sm = x_seq.reshape(B, T // L, L, -1).transpose(0, 1).contiguous()
+            out, last_hidden, memory, aux = self._run(x_sm, True, c_init, reset_memory, return_routes)
+            return out.transpose(0, 1).reshape(B, T, -1), last_hidden, memory, aux
+        return self._run(x_seq, False, c_init, reset_memory, return_routes)
+
+    @torch.no_grad()
+    def forward_segment_major(self, x_sm: Tensor, c_init: Optional[Tensor] = None, reset_memory: bool = False,
+                              return_routes: bool = False):
+        """The same on ``x_sm [T/L, B, L, D]`` (segment ``i`` of every batch row contiguous), outputs in
+        the same layout.  The kernels take one segment of all batch rows at a time, so a caller that
+        keeps this layout across layers saves the two transpositions per layer."""
+        if x_sm.dim() != 4 or x_sm.shape[2] != self.segment_length:
+            raise ValueError("expected [segments, B, segment_length, D]")
+        return self._run(x_sm.contiguous(), True, c_init, reset_memory, return_routes)
+
+    def _run(self, x: Tensor, segment_major: bool, c_init: Optional[Tensor], reset_memory: bool,
+             return_routes: bool):
+        """``x``: ``[n, B, L, D]`` when ``segment_major`` (all segments full), else ``[B, T, D]``."""
+        if x.device.type != "cuda":
+            raise RuntimeError("SegmentMemoryRunner needs CUDA tensors; this engine has no CPU path")
+        L = self.segment_length
+        if segment_major:
+            n_seg, B = x.shape[0], x.shape[1]
+            bounds = [(i * L, (i + 1) * L) for i in range(n_seg)]
+        else:
+            B, T, _ = x.shape
+            bounds = [(s0, min(s0 + L, T)) for s0 in range(0, T, L)]
         if reset_memory:
             self.clear_memory()
         if self.archive is None:
             self.archive = SegmentMemoryArchive(B, self.capacity, self.hidden, self.key_dim, self.input_size,
-                                                x_seq.device)
+                                                x.device)
         archive = self.archive
-        if x_seq.dtype == torch.bfloat16 and self.dense_retrieval:
+        if x.dtype == torch.bfloat16 and self.dense_retrieval:
             archive.keep_bf16_copy()
         # the carried state stays fp32 whatever the activations are
         memory = c_init.float() if c_init is not None else torch.zeros(B, self.hidden, self.key_dim,
-                                                                       device=x_seq.device, dtype=torch.float32)
-        if x_seq.dtype == torch.float32:
-            memory = memory.float()
+                                                                       device=x.device, dtype=torch.float32)
         # Everything that depends on the layer input alone is computed for the whole sequence at once
         # (paper_grm.py:491-493, 522-523, 566-570 do it segment by segment): the three projections of
         # the memory cell, the routing queries and the segment summaries.  Only the scan, the routing
         # against the archive and the retrieval are sequential in the segments.
-        L = self.segment_length
-        bounds = [(s0, min(s0 + L, T)) for s0 in range(0, T, L)]
 
         def per_segment(t: Tensor) -> List[Tensor]:
-            if T % L == 0 and T > 0:
-                stacked = t.reshape(B, T // L, L, t.shape[-1]).transpose(0, 1).contiguous()
-                return [stacked[i] for i in range(T // L)]
+            if segment_major:
+                return list(t.unbind(0))
             return [t[:, s0:s1].contiguous() for s0, s1 in bounds]
 
-        k_seg = per_segment(F.normalize(_linear(x_seq, self.p, "memory_cell.key_proj"), p=2, dim=-1, eps=1e-6))
-        v_seg = per_segment(_linear(x_seq, self.p, "memory_cell.value_proj"))
-        q_seg = per_segment(F.normalize(_linear(x_seq, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6))
-        x_f32 = x_seq.float()
-        if T % L == 0 and T > 0:
-            summaries = x_f32.reshape(B, T // L, L, -1).mean(dim=2)
+        k_seg = per_segment(F.normalize(_linear(x, self.p, "memory_cell.key_proj"), p=2, dim=-1, eps=1e-6))
+        v_seg = per_segment(_linear(x, self.p, "memory_cell.value_proj"))
+        q_seg = per_segment(F.normalize(_linear(x, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6))
+        # summaries [B, n, D]: mean of the fp32 input over each segment (paper_grm.py:522-523)
+        if segment_major:
+            summaries = x.mean(dim=2, dtype=torch.float32).transpose(0, 1)
         elif bounds:
-            summaries = torch.stack([x_f32[:, s0:s1].mean(dim=1) for s0, s1 in bounds], dim=1)
+            summaries = torch.stack([x[:, s0:s1].mean(dim=1, dtype=torch.float32) for s0, s1 in bounds], dim=1)
         else:
-            summaries = x_f32.new_zeros(B, 0, x_f32.shape[-1])
+            summaries = x.new_zeros(B, 0, x.shape[-1], dtype=torch.float32)
         summary_seg = [summaries[:, i] for i in range(len(bounds))]
         # The routing keys of this call's segments are projected once, here, and archived with them
         # (the reference projects the archived summaries again in every segment, paper_grm.py:566-570;
@@ -316,8 +338,9 @@ class SegmentMemoryRunner:
         if archive.write_ahead(summaries, route_key_all):
             summary_seg = [None] * len(bounds)
         if archive.count > 0 or len(bounds) > 1:
+            x_f32 = x.float()
             rq_seg = per_segment(x_f32 if fold else F.linear(x_f32, route_q_weight))
-        del x_f32
+            del x_f32
 
         hidden_seg: List[Tensor] = []
         routes = []
@@ -328,7 +351,7 @@ class SegmentMemoryRunner:
                     # the whole ring with the number of archived segments as the visible count: the
                     # same selection as over ring[:, :count], without copying that slice
                     gates, indices = self._route(rq_seg[i], archive.route_keys,
-                                                 self._visible_counts(rq_seg[i].shape[1], archive.count, x_seq.device))
+                                                 self._visible_counts(rq_seg[i].shape[1], archive.count, x.device))
                 else:
                     gates, indices = self._route(rq_seg[i], archive.ordered_route_keys())
                 h = self._retrieve_and_fuse(q_seg[i], h_online, gates, indices)
@@ -342,10 +365,11 @@ class SegmentMemoryRunner:
                 memory = torch.zeros_like(memory)
         if hidden_seg:
             last_hidden = hidden_seg[-1][:, -1]
-            out = _linear(torch.cat(hidden_seg, dim=1), self.p, "output_proj")
+            hidden = torch.stack(hidden_seg, dim=0) if segment_major else torch.cat(hidden_seg, dim=1)
+            out = _linear(hidden, self.p, "output_proj")
         else:
-            last_hidden = torch.zeros(B, self.hidden, device=x_seq.device, dtype=x_seq.dtype)
-            out = x_seq.new_zeros(B, 0, self.p["output_proj.weight"].shape[0])
+            last_hidden = torch.zeros(B, self.hidden, device=x.device, dtype=x.dtype)
+            out = x.new_zeros(B, 0, self.p["output_proj.weight"].shape[0])
         aux = {"num_segments": archive.count, "total_pushed": archive.total_pushed}
         if return_routes:
             aux["routes"] = routes
@@ -376,13 +400,26 @@ class StackedSegmentMemoryRunner:
     @torch.no_grad()
     def forward(self, x: Tensor, reset_memory: bool = True):
         p, pre = self.params, self.prefix
+        B, T = x.shape[0], x.shape[1]
+        lengths = {layer.segment_length for layer in self.layers}
+        L = next(iter(lengths))
+        # whole segments of one length in every layer: keep segment i of all batch rows contiguous from
+        # the embedding to the last layer, so that no layer transposes its input or its output
+        segment_major = len(lengths) == 1 and T > 0 and T % L == 0
+        if segment_major:
+            x = x.reshape(B, T // L, L, *x.shape[2:]).transpose(0, 1).contiguous()
         h = F.embedding(x, p["embedding.weight"]) if self.language_model else x
         finals = []
         for i, layer in enumerate(self.layers):
-            out, _, memory, _ = layer.forward(h, reset_memory=reset_memory)
+            if segment_major:
+                out, _, memory, _ = layer.forward_segment_major(h, reset_memory=reset_memory)
+            else:
+                out, _, memory, _ = layer.forward(h, reset_memory=reset_memory)
             w, b = p.get(f"{pre}layers.{i}.layer_norm.weight"), p.get(f"{pre}layers.{i}.layer_norm.bias")
             h = F.layer_norm(out + h, (h.shape[-1],), w, b, 1e-5)       # multilayer_grm.py:88-92
             finals.append(memory)
+        if segment_major:
+            h = h.transpose(0, 1).reshape(B, T, h.shape[-1])
         y = F.linear(h, p[f"{pre}output_proj.weight"], p.get(f"{pre}output_proj.bias"))
         if self.language_model:
             y = F.linear(y, p["output_layer.weight"], p.get("output_layer.bias"))
