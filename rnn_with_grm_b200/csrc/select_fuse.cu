@@ -54,15 +54,15 @@ __device__ __forceinline__ void store_piece(T* p, const float (&in)[VEC]) {
   }
 }
 
-// Lane l owns the pieces l, l + 32, ... of the row, VEC elements each.
-template <typename T, int VEC>
+// Lane l owns the pieces l, l + 32, ... of the row, VEC elements each, kPieces of them at most
+// (kPieces * 32 * VEC >= H: short rows take fewer registers and more warps fit an SM).
+template <typename T, int VEC, int kPieces>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ indices,
                    const float* __restrict__ gates, const T* __restrict__ online,
                    const float* __restrict__ ln_weight, const float* __restrict__ ln_bias, float ln_eps,
                    T* __restrict__ out, int64_t BQ, int S, int R, int H, int mode,
                    uint32_t* __restrict__ error_word) {
-  constexpr int kPieces = kMaxPerLane / VEC;
   const int lane = threadIdx.x & 31;
   const int64_t bq = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (bq >= BQ) return;   // whole warps leave together; no CTA barrier below
@@ -96,20 +96,41 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
 #pragma unroll
     for (int j = 0; j < VEC; ++j) contrib[i][j] = 0.0f;
   }
-  for (int r = 0; r < R; ++r) {                             // gate-weighted sum in route order
-    // every lane takes part in the shuffles, whatever part of the row it owns
-    const int64_t idx = __shfl_sync(0xffffffffu, my_idx, r);
-    const float gate = __shfl_sync(0xffffffffu, my_gate, r);
-    if (idx < 0) continue;                                   // the same for all lanes
-    const T* row = cand + idx * H;
+  // kRoutes routes at a time (as many as the registers hold): their rows are all requested before
+  // the first one is used.  The sum still runs in route order.
+  constexpr int kRoutes = kPieces * VEC <= 16 ? 4 : 2;
+  for (int r0 = 0; r0 < R; r0 += kRoutes) {
+    const T* row[kRoutes];
+    float gate[kRoutes];
 #pragma unroll
-    for (int i = 0; i < kPieces; ++i) {
-      const int h = (lane + 32 * i) * VEC;
-      if (h < H) {
-        float m[VEC];
-        load_piece<T, VEC>(row + h, m);
+    for (int u = 0; u < kRoutes; ++u) {
+      // every lane takes part in the shuffles, whatever part of the row it owns
+      const int src = r0 + u < R ? r0 + u : 0;
+      const int64_t idx = __shfl_sync(0xffffffffu, my_idx, src);
+      gate[u] = __shfl_sync(0xffffffffu, my_gate, src);
+      row[u] = (r0 + u < R && idx >= 0) ? cand + idx * H : nullptr;   // the same for all lanes
+    }
+    float m[kRoutes][kPieces][VEC];
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) contrib[i][j] = fmaf(gate, m[j], contrib[i][j]);
+    for (int u = 0; u < kRoutes; ++u) {
+#pragma unroll
+      for (int i = 0; i < kPieces; ++i) {
+        const int h = (lane + 32 * i) * VEC;
+        if (row[u] != nullptr && h < H) {
+          load_piece<T, VEC>(row[u] + h, m[u][i]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) m[u][i][j] = 0.0f;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kRoutes; ++u) {
+      if (row[u] == nullptr) continue;                        // an empty route adds nothing, not even 0 * x
+#pragma unroll
+      for (int i = 0; i < kPieces; ++i) {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) contrib[i][j] = fmaf(gate[u], m[u][i][j], contrib[i][j]);
       }
     }
   }
@@ -165,14 +186,31 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
   }
 }
 
+template <typename T, int VEC, int kPieces>
+void launch_select_fuse_pieces(const void* states, const int64_t* indices, const float* gates, const void* online,
+                               const float* ln_weight, const float* ln_bias, float ln_eps, void* out, int64_t BQ,
+                               int S, int R, int H, int mode, cudaStream_t s, uint32_t* err) {
+  const int64_t blocks = (BQ + kWarpsPerCta - 1) / kWarpsPerCta;
+  select_fuse_kernel<T, VEC, kPieces><<<static_cast<unsigned>(blocks), kWarpsPerCta * 32, 0, s>>>(
+      static_cast<const T*>(states), indices, gates, static_cast<const T*>(online), ln_weight, ln_bias, ln_eps,
+      static_cast<T*>(out), BQ, S, R, H, mode, err);
+}
+
 template <typename T, int VEC>
 void launch_select_fuse(const void* states, const int64_t* indices, const float* gates, const void* online,
                         const float* ln_weight, const float* ln_bias, float ln_eps, void* out, int64_t BQ, int S,
                         int R, int H, int mode, cudaStream_t s, uint32_t* err) {
-  const int64_t blocks = (BQ + kWarpsPerCta - 1) / kWarpsPerCta;
-  select_fuse_kernel<T, VEC><<<static_cast<unsigned>(blocks), kWarpsPerCta * 32, 0, s>>>(
-      static_cast<const T*>(states), indices, gates, static_cast<const T*>(online), ln_weight, ln_bias, ln_eps,
-      static_cast<T*>(out), BQ, S, R, H, mode, err);
+  constexpr int kMost = kMaxPerLane / VEC;
+  const int needed = (H + 32 * VEC - 1) / (32 * VEC);
+#define GRMX_SELECT(P)                                                                                           \
+  launch_select_fuse_pieces<T, VEC, (P) <= kMost ? (P) : kMost>(states, indices, gates, online, ln_weight, ln_bias, \
+                                                                ln_eps, out, BQ, S, R, H, mode, s, err)
+  if (needed <= 1) GRMX_SELECT(1);
+  else if (needed <= 2) GRMX_SELECT(2);
+  else if (needed <= 4) GRMX_SELECT(4);
+  else if (needed <= 8) GRMX_SELECT(8);
+  else GRMX_SELECT(kMost);
+#undef GRMX_SELECT
 }
 
 }  // namespace
