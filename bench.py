@@ -374,6 +374,43 @@ def full_occupancy_scan(lib, device, hbm_peak, launches=5):
             "bytes": nbytes, "row_tokens_per_s": rows * T / (ms * 1e-3)}
 
 
+def segment_retrieval(lib, device, hbm_peak, launches=20):
+    """The retrieval of ONE config-4 segment with per-token routing: 8 batch rows x 512 tokens choose 4
+    of 15 archived segments (512 routing features), then pick, weight, add and normalise the 512-wide
+    candidate states (bf16) the dense apply-query has produced.  The two kernels are timed separately,
+    each as one CUDA graph of `launches` launches over rotating inputs larger than L2."""
+    from rnn_with_grm_b200 import cabi
+
+    B, C, S, D, H, R = CFG4["B"], CFG4["segment"], 15, CFG4["hidden"], CFG4["hidden"], CFG4["top_k"]
+    g = torch.Generator(device=device).manual_seed(41)
+    keys = torch.randn(B, S, D, device=device, generator=g)
+    n_sets = launches
+    queries = [torch.randn(B, C, D, device=device, generator=g) for _ in range(n_sets)]           # 8.4 MB each
+    states = [torch.randn(B, C, S, H, device=device, generator=g).to(torch.bfloat16) for _ in range(4)]  # 63 MB each
+    online = torch.randn(B, C, H, device=device, generator=g).to(torch.bfloat16)
+    ln_w, ln_b = torch.ones(H, device=device), torch.zeros(H, device=device)
+    idx = torch.empty(B, C, R, device=device, dtype=torch.int64)
+    gates = torch.empty(B, C, R, device=device)
+    fused = torch.empty(B, C, H, device=device, dtype=torch.bfloat16)
+
+    def route(i, stream):
+        cabi.check(lib.grmx_topk_route(queries[i % n_sets].data_ptr(), keys.data_ptr(), None, B, C, S, D, R,
+                                       1.0 / math.sqrt(D), 1.0, idx.data_ptr(), gates.data_ptr(), None, stream))
+
+    def select(i, stream):
+        cabi.check(lib.grmx_select_fuse(states[i % 4].data_ptr(), idx.data_ptr(), gates.data_ptr(), online.data_ptr(),
+                                        ln_w.data_ptr(), ln_b.data_ptr(), 1e-5, fused.data_ptr(), B, C, S, R, H,
+                                        cabi.BF16, cabi.FUSE_RESIDUAL_LN, stream))
+
+    route_ms = time_graph(route, launches, 3)[0] / launches
+    select_ms = time_graph(select, launches, 3)[0] / launches
+    route_bytes = 4 * (B * C * D + B * S * D)
+    select_bytes = B * C * (R + 2) * H * 2
+    return {"tokens": B * C, "candidates": S, "route_us": route_ms * 1e3, "route_gbs": route_bytes / route_ms / 1e6,
+            "select_fuse_us": select_ms * 1e3, "select_fuse_gbs": select_bytes / select_ms / 1e6,
+            "select_fuse_frac_hbm": select_bytes / select_ms / 1e6 / hbm_peak}
+
+
 def config2_backward(lib, device):
     """Gradients of the config-2 scan (grad_keys, grad_values, grad_queries, grad_memory from grad_hidden
     and grad_memory_out): three scans of the same tensor-core kernel, timed as one CUDA graph."""
@@ -458,6 +495,7 @@ def other_workloads(lib, device, hbm_peak):
     out["full_occupancy_scan"] = full_occupancy_scan(lib, device, hbm_peak)
     out["cfg2_backward"] = config2_backward(lib, device)
     out["cfg4_model"] = config4_model(device)
+    out["cfg4_segment_retrieval"] = segment_retrieval(lib, device, hbm_peak)
     torch.cuda.empty_cache()
     stream = torch.cuda.current_stream().cuda_stream
     # ---- config 3: one query per segment, causal top-4 over 32 archived 64x64 fp32 matrices ----
@@ -618,6 +656,8 @@ def main(argv=None) -> int:
                         help="time the two-kernel variant of the cut (piece-state kernel + scan over a caller workspace)")
     parser.add_argument("--full-occupancy-only", action="store_true",
                         help="run only the one-row-per-SM scan of the extras and print its figures (for profiling)")
+    parser.add_argument("--segment-retrieval-only", action="store_true",
+                        help="run only the per-token routing and select-fuse kernels of one config-4 segment (for profiling)")
     args = parser.parse_args(argv)
     args.warmup = max(args.warmup, 3)
 
@@ -643,6 +683,11 @@ def main(argv=None) -> int:
     if args.full_occupancy_only:
         from rnn_with_grm_b200 import cabi
         print(json.dumps({"full_occupancy_scan": full_occupancy_scan(cabi.load(), device, load_peaks()[0])}), flush=True)
+        return 0
+    if args.segment_retrieval_only:
+        from rnn_with_grm_b200 import cabi
+        print(json.dumps({"cfg4_segment_retrieval": segment_retrieval(cabi.load(), device, load_peaks()[0], launches=4)}),
+              flush=True)
         return 0
     try:
         result = run_engine(args, rank, world, device)

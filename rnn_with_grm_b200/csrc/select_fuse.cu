@@ -14,25 +14,33 @@ constexpr int kWarpsPerCta = 8;
 constexpr int kMaxPerLane = 32;   // register path covers H <= 1024
 constexpr int kMaxRoutes = 32;
 
-// VEC consecutive elements of a row as floats: one 16-byte load when VEC spans 16 bytes
+// VEC consecutive elements of a row: one 16-byte load when VEC spans 16 bytes.  The loaded words are
+// kept as they come (for bf16, half the registers of the floats) until they are used.
+__device__ __forceinline__ uint4 load_raw16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
 template <typename T, int VEC>
-__device__ __forceinline__ void load_piece(const T* p, float (&out)[VEC]) {
-  if constexpr (VEC == 1) {
-    if constexpr (sizeof(T) == 4) out[0] = __ldg(reinterpret_cast<const float*>(p));
-    else out[0] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
-  } else if constexpr (sizeof(T) == 4) {
-    static_assert(VEC == 4, "16 bytes of fp32");
-    const float4 v = __ldg(reinterpret_cast<const float4*>(p));
-    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+__device__ __forceinline__ void unpack_piece(const uint4& v, float (&out)[VEC]) {
+  static_assert(VEC * sizeof(T) == 16, "a 16-byte piece");
+  if constexpr (sizeof(T) == 4) {
+    out[0] = __uint_as_float(v.x); out[1] = __uint_as_float(v.y);
+    out[2] = __uint_as_float(v.z); out[3] = __uint_as_float(v.w);
   } else {
-    static_assert(VEC == 8, "16 bytes of bf16");
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {            // bf16 -> fp32 is a shift
       out[2 * j] = __uint_as_float(w[j] << 16);
       out[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
     }
+  }
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void load_piece(const T* p, float (&out)[VEC]) {
+  if constexpr (VEC == 1) {
+    if constexpr (sizeof(T) == 4) out[0] = __ldg(reinterpret_cast<const float*>(p));
+    else out[0] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(p));
+  } else {
+    unpack_piece<T, VEC>(load_raw16(p), out);
   }
 }
 
@@ -98,7 +106,7 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
   }
   // kRoutes routes at a time (as many as the registers hold): their rows are all requested before
   // the first one is used.  The sum still runs in route order.
-  constexpr int kRoutes = kPieces * VEC <= 16 ? 4 : 2;
+  constexpr int kRoutes = (VEC > 1 ? kPieces <= 4 : kPieces <= 16) ? 4 : 2;
   for (int r0 = 0; r0 < R; r0 += kRoutes) {
     const T* row[kRoutes];
     float gate[kRoutes];
@@ -110,27 +118,44 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
       gate[u] = __shfl_sync(0xffffffffu, my_gate, src);
       row[u] = (r0 + u < R && idx >= 0) ? cand + idx * H : nullptr;   // the same for all lanes
     }
-    float m[kRoutes][kPieces][VEC];
+    if constexpr (VEC > 1) {
+      uint4 raw[kRoutes][kPieces];
 #pragma unroll
-    for (int u = 0; u < kRoutes; ++u) {
+      for (int u = 0; u < kRoutes; ++u) {
 #pragma unroll
-      for (int i = 0; i < kPieces; ++i) {
-        const int h = (lane + 32 * i) * VEC;
-        if (row[u] != nullptr && h < H) {
-          load_piece<T, VEC>(row[u] + h, m[u][i]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < VEC; ++j) m[u][i][j] = 0.0f;
+        for (int i = 0; i < kPieces; ++i) {
+          const int h = (lane + 32 * i) * VEC;
+          raw[u][i] = (row[u] != nullptr && h < H) ? load_raw16(row[u] + h) : make_uint4(0u, 0u, 0u, 0u);
         }
       }
-    }
 #pragma unroll
-    for (int u = 0; u < kRoutes; ++u) {
-      if (row[u] == nullptr) continue;                        // an empty route adds nothing, not even 0 * x
+      for (int u = 0; u < kRoutes; ++u) {
+        if (row[u] == nullptr) continue;                      // an empty route adds nothing, not even 0 * x
 #pragma unroll
-      for (int i = 0; i < kPieces; ++i) {
+        for (int i = 0; i < kPieces; ++i) {
+          float m[VEC];
+          unpack_piece<T, VEC>(raw[u][i], m);
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) contrib[i][j] = fmaf(gate[u], m[u][i][j], contrib[i][j]);
+          for (int j = 0; j < VEC; ++j) contrib[i][j] = fmaf(gate[u], m[j], contrib[i][j]);
+        }
+      }
+    } else {
+      float m[kRoutes][kPieces];
+#pragma unroll
+      for (int u = 0; u < kRoutes; ++u) {
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+          const int h = lane + 32 * i;
+          float one[1] = {0.0f};
+          if (row[u] != nullptr && h < H) load_piece<T, 1>(row[u] + h, one);
+          m[u][i] = one[0];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kRoutes; ++u) {
+        if (row[u] == nullptr) continue;
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) contrib[i][0] = fmaf(gate[u], m[u][i], contrib[i][0]);
       }
     }
   }
