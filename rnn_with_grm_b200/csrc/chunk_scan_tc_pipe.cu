@@ -36,6 +36,8 @@
 // all roles drain, the error word gets bit 1, TMEM is freed and the kernel returns.
 #include <cuda.h>
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "scan.cuh"
@@ -173,6 +175,12 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   auto first_offset = [&](int g) { return (g == 0 && p.first_step_no_decay) ? 1 : 0; };
 
   // ---- set-up (all threads) ----
+  // Launched as a programmatic dependent of the kernel before it in the stream (see the host side),
+  // this grid may start while that kernel is still running: the set-up below touches no global
+  // memory, and everything after it sits behind griddepcontrol.wait, which returns once the earlier
+  // grid has completed and its writes are visible.  The first instruction lets the grid AFTER this
+  // one do the same; it takes effect when every CTA of this grid has issued it, i.e. is resident.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) {
       mbar_init(&bar_full[i], 1);
@@ -212,6 +220,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
+  asm volatile("griddepcontrol.wait;" ::: "memory");   // no-op for a launch without the attribute
 
   auto stage = [&](int c) { return smem + kOffStage + (c % kStages) * kStageBytes; };
   auto vw_buf = [&](int c) { return smem + kOffVw + (c & 1) * kTileBytes; };
@@ -637,8 +646,28 @@ int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaSt
   const int64_t blocks = p.B * split.pieces * (p.H / kD);
   if (blocks > 0x7fffffffLL) return fail(GRMX_ERR_UNSUPPORTED, "tcgen05 scan: grid too large");
   for (int x_k = 0; x_k < static_cast<int>(p.K); x_k += kD) {
-    linear_scan_tc_pipe_kernel<<<static_cast<unsigned>(blocks), kThreads, kSmemAlloc, stream>>>(
-        map_q, map_k, map_v, map_o, p, split, x_k, x_k > 0 ? 1 : 0, device_error_word_ptr());
+    // programmatic stream serialisation: the set-up of this grid (barriers, TMEM, decay tables) and its
+    // launch latency overlap the tail of the kernel before it; GRMX_SCAN_PDL=off launches plainly
+    static const bool pdl = [] {
+      const char* e = getenv("GRMX_SCAN_PDL");
+      return e == nullptr || strcmp(e, "off") != 0;
+    }();
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(blocks));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = kSmemAlloc;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = pdl ? 1 : 0;
+    const cudaError_t launched =
+        cudaLaunchKernelEx(&config, linear_scan_tc_pipe_kernel, map_q, map_k, map_v, map_o, p, split, x_k,
+                           x_k > 0 ? 1 : 0, device_error_word_ptr());
+    if (launched != cudaSuccess) {
+      return fail(GRMX_ERR_LAUNCH, "linear_scan_tcgen05_pipe: launch failed: %s", cudaGetErrorString(launched));
+    }
     const int rc = check_launch("linear_scan_tcgen05_pipe");
     if (rc != GRMX_OK) return rc;
   }
