@@ -41,6 +41,9 @@ class SegmentMemoryArchive:
 
     def __init__(self, batch: int, capacity: int, hidden: int, key_dim: int, summary_dim: int, device):
         self.capacity = int(capacity)
+        if torch.device(device).type == "cuda" and not cuda_ops.load_grm_cuda_extension():
+            raise RuntimeError("the grm_cuda extension is not loaded: " +
+                               str(cuda_ops.get_grm_cuda_runtime_status().get("load_error")))
         self.memories = torch.empty(batch, self.capacity, hidden, key_dim, device=device, dtype=torch.float32)
         self.summaries = torch.empty(batch, self.capacity, summary_dim, device=device, dtype=torch.float32)
         # the summaries as the router scores them (projected once, when the segment is archived)
@@ -101,6 +104,51 @@ class SegmentMemoryArchive:
         order = (torch.arange(self.count, device=self.summaries.device) + self.head) % self.capacity
         return self.summaries.index_select(1, order)
 
+    # ---- checkpoint / resume in the reference's layout ----------------------------------------
+
+    def get_extra_state(self) -> dict:
+        """The archived segments as the reference's ``SegmentMemoryArchive.get_extra_state`` lays them
+        out (paper_grm.py:98-114): per batch size, the memories ``[B, H, K]`` and summaries ``[B, D]``
+        oldest first.  ``checkpoints`` (inputs kept for selective recomputation, which this engine does
+        not do) is an empty list."""
+        slots = [(self.head + i) % self.capacity for i in range(self.count)]
+        batch = int(self.memories.shape[0])
+        return {"groups": {batch: {"memories": [self.memories[:, s].clone() for s in slots],
+                                   "summaries": [self.summaries[:, s].clone() for s in slots],
+                                   "checkpoints": []}}}
+
+    def set_extra_state(self, state: Optional[dict]) -> None:
+        """Refill the ring from a state saved by this class or by the reference (paper_grm.py:116-133).
+        Only the group of this archive's batch size is read; more segments than the capacity keep the
+        newest.  The routing keys are left for the runner to project again."""
+        self.count = self.head = 0
+        self.route_keys = None
+        self.memories_bf16 = None
+        groups = {} if state is None else state.get("groups", {})
+        batch = int(self.memories.shape[0])
+        group = groups.get(batch, groups.get(str(batch)))
+        if group is None:
+            return
+        memories, summaries = list(group.get("memories", [])), list(group.get("summaries", []))
+        if len(memories) != len(summaries):
+            raise ValueError("extra state holds a different number of memories and summaries")
+        for memory, summary in zip(memories, summaries):
+            if tuple(memory.shape) != tuple(self.memories.shape[0:1] + self.memories.shape[2:]):
+                raise ValueError(f"archived memory of shape {tuple(memory.shape)} does not fit this archive")
+            device = self.memories.device
+            self.push(memory.to(device=device, dtype=torch.float32).contiguous(), summary.to(device=device))
+            self.total_pushed -= 1      # restoring is not pushing; the reference keeps this counter in its state_dict
+
+    def set_route_keys(self, keys: Tensor) -> None:
+        """Routing keys ``[B, count, D_route]`` of the archived segments, oldest first."""
+        if keys.shape[1] != self.count:
+            raise ValueError("one routing key per archived segment")
+        buffer = torch.empty(self.summaries.shape[0], self.capacity, keys.shape[-1], device=self.summaries.device,
+                             dtype=torch.float32)
+        slots = (torch.arange(self.count, device=buffer.device) + self.head) % self.capacity
+        buffer.index_copy_(1, slots, keys.to(torch.float32))
+        self.route_keys = buffer
+
     def ordered_route_keys(self) -> Tensor:
         """``[B, count, D_route]`` in FIFO order."""
         if self.head == 0:
@@ -156,6 +204,25 @@ class SegmentMemoryRunner:
 
     def clear_memory(self) -> None:
         self.archive = None
+
+    def get_extra_state(self) -> dict:
+        """The archive in the reference's checkpoint layout (see ``SegmentMemoryArchive.get_extra_state``)."""
+        return {"groups": {}} if self.archive is None else self.archive.get_extra_state()
+
+    def set_extra_state(self, state: Optional[dict], device=None) -> None:
+        """Resume from a saved archive: the next ``forward(..., reset_memory=False)`` retrieves from it."""
+        groups = {} if state is None else state.get("groups", {})
+        if not groups:
+            self.archive = None
+            return
+        batch, group = next(iter(groups.items()))
+        memories = group.get("memories", [])
+        if not memories:
+            self.archive = None
+            return
+        device = memories[0].device if device is None else torch.device(device)
+        self.archive = SegmentMemoryArchive(int(batch), self.capacity, self.hidden, self.key_dim, self.input_size, device)
+        self.archive.set_extra_state({"groups": {int(batch): group}})
 
     def _fp32_param(self, name: str) -> Optional[Tensor]:
         """The parameter as the kernels read it (fp32), converted once per parameter tensor."""
@@ -335,6 +402,8 @@ class SegmentMemoryRunner:
         self._route_query_weight = route_q_weight if fold else None
         route_key_all = self._route_keys(summaries)
         route_key_seg = [route_key_all[:, i] for i in range(len(bounds))]
+        if archive.count > 0 and archive.route_keys is None:       # an archive restored from a saved state
+            archive.set_route_keys(self._route_keys(archive.ordered_summaries()))
         if archive.write_ahead(summaries, route_key_all):
             summary_seg = [None] * len(bounds)
         if archive.count > 0 or len(bounds) > 1:

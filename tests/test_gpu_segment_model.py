@@ -73,6 +73,36 @@ def test_archive_ring_keeps_fifo_order_after_eviction():
     assert picked == [2.0, 4.0] and int(phys[0, 0, 2]) == -1
 
 
+def test_resume_from_extra_state_equals_the_uninterrupted_run(golden):
+    """Two segments, save the archive in the reference's checkpoint layout (paper_grm.py:98-133), load it
+    into a fresh runner, carry the state over: the rest of the sequence comes out bit for bit."""
+    g = golden("model_cfg1")
+    x = torch.from_numpy(g["x"]).to(DEV)
+    whole, _, memory_whole, _ = _runner(g).forward(x, reset_memory=True)
+    first = _runner(g)
+    out_a, _, carried, _ = first.forward(x[:, :256], reset_memory=True)
+    state = first.get_extra_state()
+    group = state["groups"][2]
+    assert len(group["memories"]) == len(group["summaries"]) == 2 and group["checkpoints"] == []
+    assert tuple(group["memories"][0].shape) == (2, 128, 64) and tuple(group["summaries"][0].shape) == (2, 2)
+    moved = {"groups": {2: {"memories": [m.cpu() for m in group["memories"]],          # as torch.load would hand it over
+                            "summaries": [t.cpu() for t in group["summaries"]], "checkpoints": []}}}
+    second = _runner(g)
+    second.set_extra_state(moved, device=DEV)
+    out_b, _, memory_b, aux = second.forward(x[:, 256:], c_init=carried, reset_memory=False)
+    assert aux["num_segments"] == 4
+    assert torch.equal(torch.cat([out_a, out_b], dim=1), whole) and torch.equal(memory_b, memory_whole)
+    # a ring that has wrapped saves its segments oldest first
+    archive = SegmentMemoryArchive(batch=2, capacity=3, hidden=4, key_dim=4, summary_dim=2, device=DEV)
+    for i in range(5):
+        archive.push(torch.full((2, 4, 4), float(i), device=DEV), torch.full((2, 2), float(i), device=DEV))
+    saved = archive.get_extra_state()["groups"][2]
+    assert [float(m[0, 0, 0]) for m in saved["memories"]] == [2.0, 3.0, 4.0]
+    again = SegmentMemoryArchive(batch=2, capacity=2, hidden=4, key_dim=4, summary_dim=2, device=DEV)
+    again.set_extra_state({"groups": {2: saved}})                # a smaller ring keeps the newest
+    assert again.count == 2 and again.ordered_summaries()[0, :, 0].tolist() == [3.0, 4.0]
+
+
 def test_eviction_does_not_change_results_when_capacity_suffices(golden):
     g = golden("model_cfg1")
     x = torch.from_numpy(g["x"]).to(DEV)
