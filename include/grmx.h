@@ -286,6 +286,18 @@ int grmx_select_fuse(const void* states, const int64_t* indices, const float* ga
                      int64_t Q, int64_t S, int64_t R, int64_t H, int dtype, int mode, void* stream);
 
 /*
+ * out[n,:] = x[n,:] / max(||x[n,:]||_2, eps) for N rows of K elements, in one pass (fp32 sum of squares).
+ * (in_dtype, out_dtype) is (F32,F32), (BF16,BF16) or (F32,BF16): the last also rounds to the type the
+ * tensor-core scan reads.  Rows must be whole 16-byte pieces (K % 4 == 0 for fp32, K % 8 == 0 for bf16),
+ * at most 128 of them, and x / out 16-byte aligned; otherwise GRMX_ERR_UNSUPPORTED.  out may alias x
+ * when the two types are equal.
+ * Replaces F.normalize(key_proj(x)) / F.normalize(query_proj(x)) (grm/core/paper_grm.py:491-493, 301, 312);
+ * the reference has no native counterpart.
+ */
+int grmx_normalize_rows(const void* x, void* out, int64_t N, int64_t K, float eps, int in_dtype, int out_dtype,
+                        void* stream);
+
+/*
  * archive[b, slot, :] = memory[b, :] and, when archive_bf16 is not NULL, the same values rounded to
  * bf16 into archive_bf16[b, slot, :].  memory float32 [B,row_elems] (row_elems = H*K), archive float32
  * [B,S,row_elems], archive_bf16 bf16 [B,S,row_elems] or NULL.  One pass over the state: the bf16 ring is

@@ -43,6 +43,7 @@ CUDA_SOURCES = [
     "retrieve_fuse.cu",
     "select_fuse.cu",
     "archive_push.cu",
+    "normalize_rows.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -303,6 +303,22 @@ at::Tensor select_fuse_cuda(const at::Tensor& states, const at::Tensor& indices,
   return out;
 }
 
+at::Tensor l2_normalize_cuda(const at::Tensor& x, double eps, bool to_bfloat16) {
+  TORCH_CHECK(x.is_cuda(), "l2_normalize needs a CUDA tensor");
+  TORCH_CHECK(x.dim() >= 1, "l2_normalize needs at least one dimension");
+  TORCH_CHECK(x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16, "l2_normalize takes float32 or bfloat16");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto in = x.contiguous();
+  const bool cast = to_bfloat16 && in.scalar_type() == at::kFloat;
+  auto out = at::empty_like(in, cast ? in.options().dtype(at::kBFloat16) : in.options());
+  const int64_t K = in.size(-1);
+  const int64_t N = K == 0 ? 0 : in.numel() / K;
+  check_status(grmx_normalize_rows(in.data_ptr(), out.data_ptr(), N, K, static_cast<float>(eps),
+                                   in.scalar_type() == at::kFloat ? GRMX_F32 : GRMX_BF16,
+                                   out.scalar_type() == at::kFloat ? GRMX_F32 : GRMX_BF16, current_stream()));
+  return out;
+}
+
 void archive_push_cuda(const at::Tensor& memory, at::Tensor archive, c10::optional<at::Tensor> shadow, int64_t slot) {
   TORCH_CHECK(archive.dim() == 4 && memory.dim() == 3, "memory [B, H, K] goes into archive [B, S, H, K]");
   TORCH_CHECK(memory.is_cuda() && archive.is_cuda(), "archive_push needs CUDA tensors");
@@ -387,6 +403,7 @@ TORCH_LIBRARY(grmx, m) {
   m.def("linear_scan(Tensor keys, Tensor values, Tensor queries, Tensor memory, float decay, float update_coeff, float hidden_scale, float memory_out_scale, bool reverse, bool first_step_no_decay, int path) -> (Tensor hidden, Tensor memory_out)");
   m.def("topk_route(Tensor queries, Tensor keys, Tensor? visible, int top_k, float scale, float temperature, bool return_scores) -> (Tensor gates, Tensor indices, Tensor scores)");
   m.def("retrieve_fuse(Tensor archive, Tensor indices, Tensor? gates, Tensor queries, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
+  m.def("l2_normalize(Tensor x, float eps, bool to_bfloat16) -> Tensor");
   m.def("archive_push(Tensor memory, Tensor(a!) archive, Tensor(b!)? shadow, int slot) -> ()");
   m.def("select_fuse(Tensor states, Tensor indices, Tensor gates, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
 }
@@ -397,6 +414,7 @@ TORCH_LIBRARY_IMPL(grmx, CUDA, m) {
   m.impl("retrieve_fuse", retrieve_fuse_cuda);
   m.impl("select_fuse", select_fuse_cuda);
   m.impl("archive_push", archive_push_cuda);
+  m.impl("l2_normalize", l2_normalize_cuda);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

@@ -167,6 +167,15 @@ def _linear(x: Tensor, params: Dict[str, Tensor], name: str) -> Tensor:
     return F.linear(x, params[f"{name}.weight"], params.get(f"{name}.bias"))
 
 
+def _l2_normalized(t: Tensor) -> Tensor:
+    """``F.normalize(t, p=2, dim=-1, eps=1e-6)`` (paper_grm.py:491-493) in one pass over ``t``."""
+    per16 = 16 // t.element_size()
+    K = t.shape[-1]
+    if t.is_cuda and t.dtype in (torch.float32, torch.bfloat16) and K % per16 == 0 and K // per16 <= 128:
+        return torch.ops.grmx.l2_normalize(t, 1e-6, False)
+    return F.normalize(t, p=2, dim=-1, eps=1e-6)
+
+
 class SegmentMemoryRunner:
     """One segment-memory layer: scan -> route -> retrieve + fuse -> output projection."""
 
@@ -381,9 +390,9 @@ class SegmentMemoryRunner:
                 return list(t.unbind(0))
             return [t[:, s0:s1].contiguous() for s0, s1 in bounds]
 
-        k_seg = per_segment(F.normalize(_linear(x, self.p, "memory_cell.key_proj"), p=2, dim=-1, eps=1e-6))
+        k_seg = per_segment(_l2_normalized(_linear(x, self.p, "memory_cell.key_proj")))
         v_seg = per_segment(_linear(x, self.p, "memory_cell.value_proj"))
-        q_seg = per_segment(F.normalize(_linear(x, self.p, "memory_cell.query_proj"), p=2, dim=-1, eps=1e-6))
+        q_seg = per_segment(_l2_normalized(_linear(x, self.p, "memory_cell.query_proj")))
         # summaries [B, n, D]: mean of the fp32 input over each segment (paper_grm.py:522-523)
         if segment_major:
             summaries = x.mean(dim=2, dtype=torch.float32).transpose(0, 1)

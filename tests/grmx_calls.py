@@ -161,3 +161,12 @@ def archive_push(memory, archive, shadow, slot):
     B, S, H, K = archive.shape
     cabi.check(lib.grmx_archive_push(cabi.ptr(memory), cabi.ptr(archive), cabi.ptr(shadow), B, S, slot, H * K,
                                      cabi.current_stream()))
+
+
+def normalize_rows(x, eps=1e-6, out_dtype=None):
+    lib = cabi.load()
+    out = torch.empty_like(x, dtype=out_dtype or x.dtype)
+    K = x.shape[-1]
+    cabi.check(lib.grmx_normalize_rows(cabi.ptr(x), cabi.ptr(out), x.numel() // K, K, float(eps),
+                                       cabi.dtype_code(x.dtype), cabi.dtype_code(out.dtype), cabi.current_stream()))
+    return out

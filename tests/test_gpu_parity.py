@@ -246,6 +246,29 @@ def test_archive_push_writes_the_slot_and_its_bf16_copy(H, K):
     assert rc == 1 and b"slot" in lib.grmx_last_error()        # GRMX_ERR_ARG, nothing launched
 
 
+@pytest.mark.parametrize("N,K", [(1, 8), (7, 64), (1000, 64), (33, 128), (5, 512), (64, 24)])
+def test_normalize_rows_matches_normalize_in_float64(N, K):
+    rng = np.random.default_rng(71 + K)
+    x = rng.standard_normal((N, K)).astype(np.float32)
+    x[0] = 0.0                                                 # a zero row stays zero (the eps clamp)
+    if N > 2:
+        x[2] *= 1e-9                                           # norm below eps: divided by eps, not by the norm
+    def want(v):
+        v = v.astype(np.float64)
+        return v / np.maximum(np.linalg.norm(v, axis=-1, keepdims=True), 1e-6)
+    close(gx.normalize_rows(dev(x)), want(x), FP32_TOL)
+    xb = dev(x, torch.bfloat16)
+    close(gx.normalize_rows(xb), want(host(xb)), LOWP_TOL)
+    close(gx.normalize_rows(dev(x), out_dtype=torch.bfloat16), want(x), LOWP_TOL)
+    inplace = dev(x)
+    lib = cabi.load()
+    cabi.check(lib.grmx_normalize_rows(cabi.ptr(inplace), cabi.ptr(inplace), N, K, 1e-6, cabi.F32, cabi.F32,
+                                       cabi.current_stream()))
+    assert torch.equal(inplace, gx.normalize_rows(dev(x)))
+    rc = lib.grmx_normalize_rows(cabi.ptr(inplace), cabi.ptr(inplace), 1, 6, 1e-6, cabi.F32, cabi.F32, cabi.current_stream())
+    assert rc == 2 and b"16-byte" in lib.grmx_last_error()      # GRMX_ERR_UNSUPPORTED: the caller keeps F.normalize
+
+
 # --------------------------------------------------------------------------- routing
 
 def test_topk_route_bit_exact_against_c_oracle():
