@@ -474,6 +474,33 @@ class StackedSegmentMemoryRunner:
             sub = {k[len(base):]: v for k, v in params.items() if k.startswith(base)}
             self.layers.append(SegmentMemoryRunner(sub, **layer_kwargs))
         self.num_layers = num_layers
+        self._unit_routes: Dict[Tuple[int, str], Tuple[Tensor, Tensor]] = {}
+        self._fp32_cache: Dict[int, Tuple[Tensor, Tensor, int]] = {}
+
+    def _add_layer_norm(self, out: Tensor, h: Tensor, weight: Optional[Tensor], bias: Optional[Tensor]) -> Tensor:
+        """``LayerNorm(out + h)`` in one pass: the residual rule of the fusion kernel with ``out`` as the
+        only candidate state and a unit gate (sum and normalisation in fp32, no rounded intermediate)."""
+        H = h.shape[-1]
+        if not (h.is_cuda and h.dtype == out.dtype and h.dtype in (torch.float32, torch.bfloat16) and H <= 1024
+                and weight is not None and bias is not None):
+            return F.layer_norm(out + h, (H,), weight, bias, 1e-5)
+        tokens = h.numel() // H
+        key = (tokens, str(h.device))
+        unit = self._unit_routes.get(key)
+        if unit is None:
+            unit = (torch.zeros(1, tokens, 1, device=h.device, dtype=torch.int64),
+                    torch.ones(1, tokens, 1, device=h.device, dtype=torch.float32))
+            self._unit_routes[key] = unit
+        params = []
+        for t in (weight, bias):
+            cached = self._fp32_cache.get(id(t))
+            if cached is None or cached[0] is not t or cached[2] != t._version:
+                cached = (t, t.float(), t._version)
+                self._fp32_cache[id(t)] = cached
+            params.append(cached[1])
+        fused = torch.ops.grmx.select_fuse(out.reshape(1, tokens, 1, H), unit[0], unit[1], h.reshape(1, tokens, H),
+                                           params[0], params[1], 1e-5, FUSE_RESIDUAL_LN)
+        return fused.view(h.shape)
 
     @torch.no_grad()
     def forward(self, x: Tensor, reset_memory: bool = True):
@@ -494,7 +521,7 @@ class StackedSegmentMemoryRunner:
             else:
                 out, _, memory, _ = layer.forward(h, reset_memory=reset_memory)
             w, b = p.get(f"{pre}layers.{i}.layer_norm.weight"), p.get(f"{pre}layers.{i}.layer_norm.bias")
-            h = F.layer_norm(out + h, (h.shape[-1],), w, b, 1e-5)       # multilayer_grm.py:88-92
+            h = self._add_layer_norm(out, h, w, b)                      # multilayer_grm.py:88-92
             finals.append(memory)
         if segment_major:
             h = h.transpose(0, 1).reshape(B, T, h.shape[-1])
