@@ -237,6 +237,19 @@ int grmx_topk_route(const float* queries, const float* keys, const int32_t* visi
                     float* scores_out, void* stream);
 
 /*
+ * grmx_topk_route with the queries stored as bf16 (keys stay fp32): per-token routing reads the layer
+ * input as it is, without an fp32 copy of it.  The queries are widened while they are staged, which is
+ * exact, so scores, indices and gates are those of grmx_topk_route on the widened queries, bit for bit.
+ * Covers the per-token shapes only: 1 <= S <= 16 keys, Q >= 64 queries per batch row, D % 8 == 0,
+ * D <= 1024, B <= 65535, 16-byte aligned inputs; GRMX_ERR_UNSUPPORTED otherwise (widen and call
+ * grmx_topk_route).  Same reference code as grmx_topk_route.
+ */
+int grmx_topk_route_bf16q(const void* queries_bf16, const float* keys, const int32_t* visible,
+                          int64_t B, int64_t Q, int64_t S, int64_t D, int top_k, float scale,
+                          float temperature, int64_t* indices_out, float* gates_out,
+                          float* scores_out, void* stream);
+
+/*
  * Selection and gates only, on scores the caller already holds (for example
  * after applying an attention mask with -inf): same rules as grmx_topk_route
  * from "visible" onwards.  scores fp32 [B,Q,S].

@@ -65,6 +65,10 @@ SIGNATURES = {
         c_int,
         [c_void_p] * 3 + [c_int64] * 4 + [c_int, c_float, c_float] + [c_void_p] * 3 + [c_void_p],
     ),
+    "grmx_topk_route_bf16q": (
+        c_int,
+        [c_void_p] * 3 + [c_int64] * 4 + [c_int, c_float, c_float] + [c_void_p] * 3 + [c_void_p],
+    ),
     "grmx_topk_select": (
         c_int,
         [c_void_p, c_void_p] + [c_int64] * 3 + [c_int, c_float] + [c_void_p] * 2 + [c_void_p],

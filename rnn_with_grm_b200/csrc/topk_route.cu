@@ -104,10 +104,11 @@ __host__ __device__ constexpr size_t few_keys_smem_bytes(int D, int queries_per_
   return sizeof(float) * ((size_t)D * kFewKeys + (size_t)queries_per_cta * (D + kFewPad));
 }
 
-// kFewChains queries per half-warp, kFewWarps warps per CTA
-template <int kFewChains, int kFewWarps>
+// kFewChains queries per half-warp, kFewWarps warps per CTA; TQ: the queries as stored, float or
+// bf16 (widened while they are staged, which is exact: the scores do not depend on it)
+template <int kFewChains, int kFewWarps, typename TQ>
 __global__ void __launch_bounds__(kFewWarps * 32)
-topk_route_few_keys_kernel(const float* __restrict__ queries, const float* __restrict__ keys,
+topk_route_few_keys_kernel(const TQ* __restrict__ queries, const float* __restrict__ keys,
                            const int32_t* __restrict__ visible, int64_t Q, int S, int D, int top_k,
                            float scale, float temperature, int64_t* __restrict__ indices_out,
                            float* __restrict__ gates_out, float* __restrict__ scores_out) {
@@ -129,21 +130,48 @@ topk_route_few_keys_kernel(const float* __restrict__ queries, const float* __res
   // lane in flight; rows past the last query are filled with zeros and dropped below
   const int64_t first = q0 + warp * kFewPerWarp;
   const int64_t rows_here = Q - first < kFewPerWarp ? (Q - first > 0 ? Q - first : 0) : kFewPerWarp;
-  const int n_valid = (int)rows_here * D4;
-  const float4* qsrc = reinterpret_cast<const float4*>(queries + (b * Q + first) * D);
-  for (int e0 = lane; e0 < kFewPerWarp * D4; e0 += 32 * 8) {
-    float4 t[8];
+  if constexpr (sizeof(TQ) == 4) {
+    const int n_valid = (int)rows_here * D4;
+    const float4* qsrc = reinterpret_cast<const float4*>(queries + (b * Q + first) * D);
+    for (int e0 = lane; e0 < kFewPerWarp * D4; e0 += 32 * 8) {
+      float4 t[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = e0 + 32 * i;
-      t[i] = e < n_valid ? __ldg(qsrc + e) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      for (int i = 0; i < 8; ++i) {
+        const int e = e0 + 32 * i;
+        t[i] = e < n_valid ? __ldg(qsrc + e) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = e0 + 32 * i;
+        if (e < kFewPerWarp * D4) {
+          const int slot = e / D4;
+          s_q[slot * row4 + (e - slot * D4)] = t[i];
+        }
+      }
     }
+  } else {
+    // bf16 rows (D % 8 == 0): 16 bytes are eight features, two float4 of the staged row
+    const int D8 = D >> 3;
+    const int n_valid = (int)rows_here * D8;
+    const uint4* qsrc = reinterpret_cast<const uint4*>(queries + (b * Q + first) * D);
+    for (int e0 = lane; e0 < kFewPerWarp * D8; e0 += 32 * 8) {
+      uint4 t[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = e0 + 32 * i;
-      if (e < kFewPerWarp * D4) {
-        const int slot = e / D4;
-        s_q[slot * row4 + (e - slot * D4)] = t[i];
+      for (int i = 0; i < 8; ++i) {
+        const int e = e0 + 32 * i;
+        t[i] = e < n_valid ? __ldg(qsrc + e) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = e0 + 32 * i;
+        if (e < kFewPerWarp * D8) {
+          const int slot = e / D8;
+          float4* dst = s_q + slot * row4 + 2 * (e - slot * D8);
+          dst[0] = make_float4(__uint_as_float(t[i].x << 16), __uint_as_float(t[i].x & 0xffff0000u),
+                               __uint_as_float(t[i].y << 16), __uint_as_float(t[i].y & 0xffff0000u));
+          dst[1] = make_float4(__uint_as_float(t[i].z << 16), __uint_as_float(t[i].z & 0xffff0000u),
+                               __uint_as_float(t[i].w << 16), __uint_as_float(t[i].w & 0xffff0000u));
+        }
       }
     }
   }
@@ -287,17 +315,17 @@ topk_route_kernel(const float* __restrict__ queries, const float* __restrict__ k
 
 namespace grmx {
 namespace {
-template <int kChains, int kWarps>
-int launch_few_keys(const float* queries, const float* keys, const int32_t* visible, int64_t B, int64_t Q, int64_t S,
+template <int kChains, int kWarps, typename TQ>
+int launch_few_keys(const TQ* queries, const float* keys, const int32_t* visible, int64_t B, int64_t Q, int64_t S,
                     int64_t D, int top_k, float scale, float temperature, int64_t* indices_out, float* gates_out,
                     float* scores_out, cudaStream_t stream) {
   constexpr int per_cta = 2 * kChains * kWarps;
   static const cudaError_t opted =
-      cudaFuncSetAttribute(topk_route_few_keys_kernel<kChains, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaFuncSetAttribute(topk_route_few_keys_kernel<kChains, kWarps, TQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(few_keys_smem_bytes(kFewMaxD, per_cta)));
   GRMX_REQUIRE(opted == cudaSuccess, "grmx_topk_route: shared-memory opt-in failed: %s", cudaGetErrorString(opted));
   const dim3 grid(static_cast<unsigned>((Q + per_cta - 1) / per_cta), static_cast<unsigned>(B));
-  topk_route_few_keys_kernel<kChains, kWarps><<<grid, kWarps * 32, few_keys_smem_bytes(static_cast<int>(D), per_cta), stream>>>(
+  topk_route_few_keys_kernel<kChains, kWarps, TQ><<<grid, kWarps * 32, few_keys_smem_bytes(static_cast<int>(D), per_cta), stream>>>(
       queries, keys, visible, Q, static_cast<int>(S), static_cast<int>(D), top_k, scale, temperature, indices_out,
       gates_out, scores_out);
   return check_launch("topk_route_few_keys");
@@ -324,7 +352,7 @@ extern "C" int grmx_topk_route(const float* queries, const float* keys, const in
   if (S >= 1 && S <= kFewKeys && Q >= 64 && D >= 4 && D % 4 == 0 && D <= kFewMaxD && aligned && B <= 65535) {
     // measured at 8 x 512 queries of 512 features: one query per half-warp and 16 warps per CTA
     // (15.9 us against 29 us with four queries per half-warp and 4 warps, 43 us for the kernel below)
-    return launch_few_keys<1, 16>(queries, keys, visible, B, Q, S, D, top_k, scale, temperature, indices_out, gates_out,
+    return launch_few_keys<1, 16, float>(queries, keys, visible, B, Q, S, D, top_k, scale, temperature, indices_out, gates_out,
                                   scores_out, static_cast<cudaStream_t>(stream));
   }
   const size_t smem = (size_t)kWarpsPerCta * S * (sizeof(float) + 1) + 16;
@@ -332,6 +360,27 @@ extern "C" int grmx_topk_route(const float* queries, const float* keys, const in
       queries, keys, visible, BQ, Q, static_cast<int>(S), static_cast<int>(D), top_k, scale,
       temperature, nullptr, indices_out, gates_out, scores_out);
   return check_launch("topk_route");
+}
+
+extern "C" int grmx_topk_route_bf16q(const void* queries_bf16, const float* keys, const int32_t* visible, int64_t B,
+                                     int64_t Q, int64_t S, int64_t D, int top_k, float scale, float temperature,
+                                     int64_t* indices_out, float* gates_out, float* scores_out, void* stream) {
+  using namespace grmx;
+  const char* who = "grmx_topk_route_bf16q";
+  GRMX_REQUIRE(B >= 0 && Q >= 0 && S >= 0 && D >= 0, "%s: negative size", who);
+  GRMX_REQUIRE(top_k >= 0 && top_k <= kMaxTopK, "%s: top_k %d outside [0, %d]", who, top_k, kMaxTopK);
+  if (B * Q == 0 || top_k == 0) return GRMX_OK;
+  GRMX_REQUIRE(indices_out && gates_out, "%s: NULL output pointer", who);
+  GRMX_REQUIRE(queries_bf16 && keys, "%s: NULL input pointer", who);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(queries_bf16) | reinterpret_cast<uintptr_t>(keys)) & 15u) == 0;
+  if (!(S >= 1 && S <= kFewKeys && Q >= 64 && D >= 8 && D % 8 == 0 && D <= kFewMaxD && aligned && B <= 65535)) {
+    return fail(GRMX_ERR_UNSUPPORTED,
+                "%s: covers 1..%d keys, at least 64 queries per batch row, D %% 8 == 0, D <= %d, 16-byte aligned "
+                "inputs; widen the queries to float32 and call grmx_topk_route otherwise", who, kFewKeys, kFewMaxD);
+  }
+  return launch_few_keys<1, 16, __nv_bfloat16>(static_cast<const __nv_bfloat16*>(queries_bf16), keys, visible, B, Q, S,
+                                               D, top_k, scale, temperature, indices_out, gates_out, scores_out,
+                                               static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int grmx_topk_select(const float* scores, const int32_t* visible, int64_t B, int64_t Q,

@@ -238,9 +238,15 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> topk_route_cuda(const at::Tensor&
   require_cuda(queries, "queries");
   require_cuda(keys, "keys");
   c10::cuda::CUDAGuard guard(queries.device());
-  auto q = queries.to(at::kFloat).contiguous();
   auto k = keys.to(at::kFloat).contiguous();
-  const int64_t B = q.size(0), Q = q.size(1), D = q.size(2), S = k.size(1);
+  const int64_t B = queries.size(0), Q = queries.size(1), D = queries.size(2), S = k.size(1);
+  // bf16 queries of the per-token shapes are read as they are (grmx_topk_route_bf16q); everything else
+  // is widened to fp32 first
+  at::Tensor q = queries.contiguous();
+  const bool lowp = q.scalar_type() == at::kBFloat16 && S >= 1 && S <= 16 && Q >= 64 && D >= 8 && D % 8 == 0 &&
+                    D <= 1024 && B <= 65535 && (reinterpret_cast<uintptr_t>(q.data_ptr()) & 15u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(k.data_ptr()) & 15u) == 0;
+  if (!lowp) q = q.to(at::kFloat);
   at::Tensor vis;
   const int32_t* vis_ptr = nullptr;
   if (visible.has_value() && visible->defined()) {
@@ -249,9 +255,17 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> topk_route_cuda(const at::Tensor&
     vis = visible->to(at::kInt).contiguous();
     vis_ptr = vis.data_ptr<int32_t>();
   }
-  auto idx = at::empty({B, Q, top_k}, q.options().dtype(at::kLong));
-  auto gates = at::empty({B, Q, top_k}, q.options());
-  at::Tensor scores = return_scores ? at::empty({B, Q, S}, q.options()) : at::empty({0}, q.options());
+  auto idx = at::empty({B, Q, top_k}, k.options().dtype(at::kLong));
+  auto gates = at::empty({B, Q, top_k}, k.options());
+  at::Tensor scores = return_scores ? at::empty({B, Q, S}, k.options()) : at::empty({0}, k.options());
+  if (lowp) {
+    check_status(grmx_topk_route_bf16q(q.data_ptr(), k.data_ptr<float>(), vis_ptr, B, Q, S, D,
+                                       static_cast<int>(top_k), static_cast<float>(scale),
+                                       static_cast<float>(temperature), idx.data_ptr<int64_t>(),
+                                       gates.data_ptr<float>(), return_scores ? scores.data_ptr<float>() : nullptr,
+                                       current_stream()));
+    return {gates, idx, scores};
+  }
   check_status(grmx_topk_route(q.data_ptr<float>(), k.data_ptr<float>(), vis_ptr, B, Q, S, D,
                                static_cast<int>(top_k), static_cast<float>(scale),
                                static_cast<float>(temperature), idx.data_ptr<int64_t>(),

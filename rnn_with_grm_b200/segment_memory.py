@@ -416,9 +416,9 @@ class SegmentMemoryRunner:
         if archive.write_ahead(summaries, route_key_all):
             summary_seg = [None] * len(bounds)
         if archive.count > 0 or len(bounds) > 1:
-            x_f32 = x.float()
-            rq_seg = per_segment(x_f32 if fold else F.linear(x_f32, route_q_weight))
-            del x_f32
+            # folded, the router scores the layer input itself; bf16 input is read as it is (widening is
+            # exact, so the scores are those of the fp32 copy)
+            rq_seg = per_segment(x if fold else F.linear(x.float(), route_q_weight))
 
         hidden_seg: List[Tensor] = []
         routes = []

@@ -114,7 +114,8 @@ def topk_route(queries, keys, top_k, scale=1.0, temperature=1.0, visible=None, w
     idx = torch.empty(B, Q, top_k, device=queries.device, dtype=torch.int64)
     gates = torch.empty(B, Q, top_k, device=queries.device, dtype=torch.float32)
     scores = torch.empty(B, Q, S, device=queries.device, dtype=torch.float32) if want_scores else None
-    cabi.check(lib.grmx_topk_route(cabi.ptr(queries), cabi.ptr(keys), cabi.ptr(visible), B, Q, S, D, top_k,
+    entry = lib.grmx_topk_route_bf16q if queries.dtype == torch.bfloat16 else lib.grmx_topk_route
+    cabi.check(entry(cabi.ptr(queries), cabi.ptr(keys), cabi.ptr(visible), B, Q, S, D, top_k,
                                    float(scale), float(temperature), cabi.ptr(idx), cabi.ptr(gates),
                                    cabi.ptr(scores), cabi.current_stream()))
     return idx, gates, scores

@@ -308,6 +308,25 @@ def test_topk_route_with_few_keys_and_many_queries_bit_exact(B, Q, S, D, top_k):
     assert cabi.device_error_word() == 0
 
 
+@pytest.mark.parametrize("B,Q,S,D,top_k", [(2, 512, 15, 512, 4), (3, 70, 5, 40, 4), (1, 97, 16, 1024, 16)])
+def test_topk_route_reads_bf16_queries_as_if_widened(B, Q, S, D, top_k):
+    rng = np.random.default_rng(53 + Q)
+    q16 = dev(rng.standard_normal((B, Q, D)).astype(np.float32), torch.bfloat16)
+    kv = dev(rng.standard_normal((B, S, D)).astype(np.float32))
+    visible = dev(rng.integers(0, S + 2, size=Q).astype(np.int32))
+    want = gx.topk_route(q16.float(), kv, top_k, 0.1, 0.9, visible)
+    got = gx.topk_route(q16, kv, top_k, 0.1, 0.9, visible)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)                               # indices, gates and scores bit for bit
+    # shapes outside the per-token case are refused, nothing runs
+    lib = cabi.load()
+    idx = torch.empty(B, 8, top_k, device=DEV, dtype=torch.int64)
+    gates = torch.empty(B, 8, top_k, device=DEV)
+    rc = lib.grmx_topk_route_bf16q(cabi.ptr(q16), cabi.ptr(kv), None, B, 8, S, D, top_k, 0.1, 0.9, cabi.ptr(idx),
+                                   cabi.ptr(gates), None, cabi.current_stream())
+    assert rc == 2 and b"widen" in lib.grmx_last_error()
+
+
 def test_topk_matches_reference_retriever_fixtures(golden):
     for name in ("topk", "identity"):
         g = golden(f"retriever_{name}")
