@@ -5,6 +5,8 @@
 // and what is left of RetrievedStateFusion (grm/core/aggregator.py:104-105, 116-118) is, per token:
 // pick R of the S candidate states, weight them by the gates, add the online state, LayerNorm.
 // One warp per token; the row stays in registers between the sum and the normalisation.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace grmx {
@@ -65,7 +67,7 @@ __device__ __forceinline__ void store_piece(T* p, const float (&in)[VEC]) {
 // Lane l owns the pieces l, l + 32, ... of the row, VEC elements each, kPieces of them at most
 // (kPieces * 32 * VEC >= H: short rows take fewer registers and more warps fit an SM).
 template <typename T, int VEC, int kPieces>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, (VEC > 1 && kPieces * VEC <= 16) ? 4 : 1)
 select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ indices,
                    const float* __restrict__ gates, const T* __restrict__ online,
                    const float* __restrict__ ln_weight, const float* __restrict__ ln_bias, float ln_eps,
@@ -90,13 +92,19 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
   const T* cand = states + bq * (int64_t)S * H;
   const bool fuse = mode == GRMX_FUSE_RESIDUAL_LN;
 
-  float x[kPieces][VEC];
+  // the online row is requested now and kept as loaded (packed) until the routes have been summed
+  using Held = typename std::conditional<(VEC > 1), uint4, float>::type;
+  Held held[kPieces];
 #pragma unroll
   for (int i = 0; i < kPieces; ++i) {
     const int h = (lane + 32 * i) * VEC;
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) x[i][j] = 0.0f;
-    if (fuse && h < H) load_piece<T, VEC>(online + bq * H + h, x[i]);
+    if constexpr (VEC > 1) {
+      held[i] = (fuse && h < H) ? load_raw16(online + bq * H + h) : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+      float one[1] = {0.0f};
+      if (fuse && h < H) load_piece<T, 1>(online + bq * H + h, one);
+      held[i] = one[0];
+    }
   }
   float contrib[kPieces][VEC];
 #pragma unroll
@@ -159,9 +167,12 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
       }
     }
   }
+  float x[kPieces][VEC];
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < kPieces; ++i) {
+    if constexpr (VEC > 1) unpack_piece<T, VEC>(held[i], x[i]);
+    else x[i][0] = held[i];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
       x[i][j] += contrib[i][j];       // online + contribution, as the reference adds them
