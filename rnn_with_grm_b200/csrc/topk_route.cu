@@ -115,8 +115,6 @@ topk_route_few_keys_kernel(const TQ* __restrict__ queries, const float* __restri
   constexpr int kFewPerWarp = 2 * kFewChains;
   constexpr int kFewPerCta = kFewWarps * kFewPerWarp;
   extern __shared__ float4 s_few[];                           // keys [D/4][kFewKeys], then queries [kFewPerCta][D/4 + 1]
-  __shared__ float s_sc[kFewPerCta][kFewKeys];
-  __shared__ uint8_t s_taken[kFewPerCta][kFewKeys];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int64_t b = blockIdx.y;
@@ -216,29 +214,57 @@ topk_route_few_keys_kernel(const TQ* __restrict__ queries, const float* __restri
       }
     }
   }
-  if (s < S) {
+  // Selection in registers, both queries of the warp at once: lane (half, s) holds the score of key s
+  // for the query of its half.  The rank of a key among the visible ones (how many beat it: higher
+  // score, or the same score and a lower index) comes from 16 independent shuffles instead of a
+  // round of dependent ones per route; the key of rank r is route r.
 #pragma unroll
-    for (int c = 0; c < kFewChains; ++c) {
-      const int slot = warp * kFewPerWarp + half * kFewChains + c;
-      const float score = acc[c] * scale;
-      s_sc[slot][s] = score;
-      s_taken[slot][s] = 0;
-      if (scores_out != nullptr && q0 + slot < Q) scores_out[(b * Q + q0 + slot) * S + s] = score;
-    }
-  }
-  __syncwarp();
-  for (int i = 0; i < kFewPerWarp; ++i) {                     // the whole warp selects for each of its queries
-    const int slot = warp * kFewPerWarp + i;
+  for (int c = 0; c < kFewChains; ++c) {
+    const int slot = warp * kFewPerWarp + half * kFewChains + c;
     const int64_t q = q0 + slot;
-    if (q >= Q) break;                                        // the same for all lanes
+    const bool query_live = q < Q;
+    const float score = acc[c] * scale;
+    if (scores_out != nullptr && query_live && s < S) scores_out[(b * Q + q) * S + s] = score;
     int n_vis = S;
-    if (visible != nullptr) {
+    if (visible != nullptr && query_live) {
       n_vis = visible[q];
       n_vis = n_vis < 0 ? 0 : (n_vis > S ? S : n_vis);
     }
-    const int64_t bq = b * Q + q;
-    select_and_gate(s_sc[slot], s_taken[slot], n_vis, top_k, temperature, lane, indices_out + bq * top_k,
-                    gates_out + bq * top_k);
+    const int R = top_k < n_vis ? top_k : n_vis;
+    const bool seen = s < n_vis;
+    const unsigned long long mine =
+        seen ? (((unsigned long long)ordered_bits(score) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)s)) : 0ull;
+    int rank = 0;
+#pragma unroll
+    for (int j = 0; j < kFewKeys; ++j) {
+      const unsigned long long other = __shfl_sync(0xffffffffu, mine, (lane & 16) | j);
+      rank += other > mine ? 1 : 0;
+    }
+    if (R == n_vis) rank = s;                                  // every visible key is taken: identity order
+    const bool chosen = seen && rank < R;
+    // softmax over the chosen scores, inside the half-warp
+    const float x = chosen ? score / temperature : -CUDART_INF_F;
+    float mx = x;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    // fmaxf drops NaN; put it back so a NaN score poisons the row as softmax does
+    const unsigned nan_mask = __ballot_sync(0xffffffffu, chosen && x != x) & (half ? 0xffff0000u : 0x0000ffffu);
+    const float e = chosen ? expf(x - mx) : 0.0f;
+    float sum = e;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (query_live) {
+      int64_t* idx_row = indices_out + (b * Q + q) * top_k;
+      float* gate_row = gates_out + (b * Q + q) * top_k;
+      if (chosen) {
+        idx_row[rank] = s;
+        gate_row[rank] = nan_mask != 0u ? CUDART_NAN_F : e / sum;
+      }
+      for (int r = R + s; r < top_k; r += kFewKeys) {          // slots without a route
+        idx_row[r] = -1;
+        gate_row[r] = 0.0f;
+      }
+    }
   }
 }
 
