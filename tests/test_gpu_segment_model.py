@@ -103,6 +103,28 @@ def test_resume_from_extra_state_equals_the_uninterrupted_run(golden):
     assert again.count == 2 and again.ordered_summaries()[0, :, 0].tolist() == [3.0, 4.0]
 
 
+def test_ragged_last_segment_and_both_layouts_agree(golden):
+    """A sequence that does not end on a segment boundary runs in the token-major layout; its result
+    must be that of whole segments followed by the remainder as a call of its own, and the two
+    layouts must agree on a sequence both can run."""
+    g = golden("model_cfg1")
+    x = torch.from_numpy(g["x"]).to(DEV)
+    runner = _runner(g)
+    ragged, h_r, mem_r, aux = runner.forward(x[:, :300], reset_memory=True)
+    assert aux["num_segments"] == 3 and ragged.shape[1] == 300
+    two = _runner(g)
+    head, _, carried, _ = two.forward(x[:, :256], reset_memory=True)
+    tail, h_t, mem_t, _ = two.forward(x[:, 256:300], c_init=carried, reset_memory=False)
+    assert go.rel_err(ragged.cpu().numpy(), torch.cat([head, tail], dim=1).cpu().numpy()) < FP32_TOL
+    assert go.rel_err(mem_r.cpu().numpy(), mem_t.cpu().numpy()) < FP32_TOL
+    assert go.rel_err(h_r.cpu().numpy(), h_t.cpu().numpy()) < FP32_TOL
+    token_major = _runner(g)._run(x, False, None, True, False)[0]
+    assert go.rel_err(token_major.cpu().numpy(), g["outputs"]) < FP32_TOL
+    # an empty sequence is a no-op that returns empty outputs
+    empty, _, _, aux0 = _runner(g).forward(x[:, :0], reset_memory=True)
+    assert empty.shape[1] == 0 and aux0["num_segments"] == 0
+
+
 def test_eviction_does_not_change_results_when_capacity_suffices(golden):
     g = golden("model_cfg1")
     x = torch.from_numpy(g["x"]).to(DEV)
