@@ -97,6 +97,23 @@ int grmx_chunk_scan_fwd(const void* keys, const void* values, const void* querie
                         int io_dtype, int state_dtype, int path, void* stream);
 
 /*
+ * grmx_chunk_scan_fwd over a sequence of T / segment_tokens whole segments in ONE launch, leaving the
+ * state at the end of segment j in archive[b, first_slot + j, :, :] (archive float32 [B, capacity, H, K],
+ * dense, 16-byte aligned) besides hidden_out and the final memory_out.  The result is that of one
+ * grmx_chunk_scan_fwd call per segment with the state carried from call to call: the reference's segment
+ * loop (grm/core/paper_grm.py:702-728, memory_initialization_mode "checkpoint") runs the scan and the
+ * archive append once per segment; the retrieval of a segment reads only earlier slots, so it can follow
+ * for all segments at once.  Tensor-core scan only (bf16 tokens, fp32 state, K and H multiples of 64),
+ * segment_tokens a multiple of 128 that divides T, first_slot + T / segment_tokens <= capacity;
+ * GRMX_ERR_UNSUPPORTED otherwise (run the segments one by one).
+ */
+int grmx_chunk_scan_fwd_segments(const void* keys, const void* values, const void* queries,
+                                 const void* memory_in, void* hidden_out, void* memory_out, float* archive,
+                                 int64_t capacity, int64_t first_slot, int64_t segment_tokens, int64_t B,
+                                 int64_t T, int64_t K, int64_t H, float decay, int io_dtype, int state_dtype,
+                                 void* stream);
+
+/*
  * grmx_chunk_scan_fwd with a caller-provided workspace: the two-kernel form of the cut along T.
  * A first kernel computes every piece's own contribution to the state into `scratch` (device
  * memory, 16-byte aligned, contents irrelevant on entry, not preserved), the scan kernel rebuilds

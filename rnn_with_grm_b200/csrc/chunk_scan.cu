@@ -128,6 +128,48 @@ int grmx_chunk_scan_fwd(const void* keys, const void* values, const void* querie
                         "grmx_chunk_scan_fwd");
 }
 
+int grmx_chunk_scan_fwd_segments(const void* keys, const void* values, const void* queries,
+                                 const void* memory_in, void* hidden_out, void* memory_out, float* archive,
+                                 int64_t capacity, int64_t first_slot, int64_t segment_tokens, int64_t B,
+                                 int64_t T, int64_t K, int64_t H, float decay, int io_dtype, int state_dtype,
+                                 void* stream) {
+  const char* who = "grmx_chunk_scan_fwd_segments";
+  if (K <= 0) return grmx::fail(GRMX_ERR_ARG, "%s: K must be positive", who);
+  if (B > 0 && (memory_out == nullptr || archive == nullptr)) {
+    return grmx::fail(GRMX_ERR_ARG, "%s: memory_out or archive is NULL", who);
+  }
+  if (segment_tokens <= 0 || segment_tokens % 128 != 0 || T % segment_tokens != 0) {
+    return grmx::fail(GRMX_ERR_UNSUPPORTED, "%s: segments must be whole multiples of 128 tokens and divide T", who);
+  }
+  const int64_t segments = T / segment_tokens;
+  if (first_slot < 0 || capacity < 0 || first_slot + segments > capacity) {
+    return grmx::fail(GRMX_ERR_ARG, "%s: slots [%lld, %lld) do not fit an archive of %lld", who, (long long)first_slot,
+                      (long long)(first_slot + segments), (long long)capacity);
+  }
+  if ((reinterpret_cast<uintptr_t>(archive) & 15u) != 0) {
+    return grmx::fail(GRMX_ERR_ARG, "%s: archive must be 16-byte aligned", who);
+  }
+  grmx::ScanParams p;
+  p.keys = keys; p.values = values; p.queries = queries; p.memory_in = memory_in;
+  p.hidden_out = hidden_out; p.memory_out = memory_out;
+  p.B = B; p.T = T; p.K = K; p.H = H;
+  p.m_row_stride = K; p.m_col_stride = 1;
+  p.decay = decay; p.update_coeff = (1.0f - decay) * (1.0f / sqrtf(static_cast<float>(K)));
+  p.hidden_scale = 1.0f; p.memory_out_scale = 1.0f; p.reverse = 0; p.first_step_no_decay = 0;
+  p.snapshots = archive + first_slot * H * K;
+  p.snap_batch_stride = capacity * H * K;
+  p.snap_stride = H * K;
+  p.snap_chunks = static_cast<int>(segment_tokens / 128);
+  const int rc = grmx::validate_scan(p, io_dtype, state_dtype, GRMX_PATH_TCGEN05, who);
+  if (rc != GRMX_OK) return rc;
+  if (B == 0 || T == 0) return GRMX_OK;
+  const char* why = "";
+  if (!grmx::scan_tcgen05_supported(p, io_dtype, state_dtype, &why) || !grmx::scan_tcgen05_pipe_supported(p)) {
+    return grmx::fail(GRMX_ERR_UNSUPPORTED, "%s: needs the tensor-core scan: %s", who, why);
+  }
+  return grmx::launch_scan_tcgen05_selfcut(p, static_cast<cudaStream_t>(stream));
+}
+
 int64_t grmx_chunk_scan_scratch_bytes(int64_t B, int64_t T, int64_t K, int64_t H, int io_dtype,
                                       int state_dtype) {
   if (B <= 0 || T <= 0 || K <= 0 || H <= 0) return 0;

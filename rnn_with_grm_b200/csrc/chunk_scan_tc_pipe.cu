@@ -437,6 +437,17 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         }
         tc_fence_before();
         mbar_arrive(&bar_u_free[c & 1]);
+        if (p.snapshots != nullptr && c >= pre && owns_row && (g0 + c + 1) % p.snap_chunks == 0) {
+          // a segment ends with this chunk: its state goes to the caller's archive
+          float* snap = p.snapshots + b * p.snap_batch_stride + ((g0 + c + 1) / p.snap_chunks - 1) * p.snap_stride +
+                        (x_v + state_row) * p.K + x_k;
+#pragma unroll
+          for (int j = 0; j < kD; j += 4) {
+            *reinterpret_cast<float4*>(snap + j) =
+                make_float4(m[j] * p.memory_out_scale, m[j + 1] * p.memory_out_scale, m[j + 2] * p.memory_out_scale,
+                            m[j + 3] * p.memory_out_scale);
+          }
+        }
         if (!last) {
           if (c + 1 >= pre) {                 // the next chunk is an own chunk: [S | R] needs the state
             if (owns_row) write_mb(c + 1);

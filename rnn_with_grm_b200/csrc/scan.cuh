@@ -20,6 +20,13 @@ struct ScanParams {
   float memory_out_scale;
   int reverse;
   int first_step_no_decay;
+  // Optional: the state after every snap_chunks * 128 tokens (forward scans whose T is a multiple of
+  // that), [H,K] fp32 dense at snapshots + b * snap_batch_stride + j * snap_stride (elements), scaled
+  // like memory_out.  Only the warp-specialised tensor-core kernel writes them.
+  float* snapshots = nullptr;
+  int64_t snap_batch_stride = 0;
+  int64_t snap_stride = 0;
+  int snap_chunks = 0;
 };
 
 // fp32 CUDA-core scan: any K <= 256, any H, any T.

@@ -317,6 +317,30 @@ at::Tensor select_fuse_cuda(const at::Tensor& states, const at::Tensor& indices,
   return out;
 }
 
+std::tuple<at::Tensor, at::Tensor> chunk_scan_segments_cuda(const at::Tensor& keys, const at::Tensor& values,
+                                                            const at::Tensor& queries, const at::Tensor& memory,
+                                                            double memory_decay, at::Tensor archive, int64_t first_slot,
+                                                            int64_t segment_tokens) {
+  check_chunk_inputs(keys, values, queries, memory);
+  TORCH_CHECK(archive.is_cuda() && archive.dim() == 4 && archive.scalar_type() == at::kFloat && archive.is_contiguous(),
+              "archive must be a contiguous float32 CUDA tensor [B, capacity, H, K]");
+  c10::cuda::CUDAGuard guard(keys.device());
+  auto k = keys.contiguous();
+  auto v = values.contiguous();
+  auto q = queries.contiguous();
+  auto m = memory.contiguous();
+  const int64_t B = k.size(0), T = k.size(1), K = k.size(2), H = v.size(2);
+  TORCH_CHECK(archive.size(0) == B && archive.size(2) == H && archive.size(3) == K, "archive does not match the scan");
+  auto hidden = at::empty({B, T, H}, v.options());
+  auto memory_out = at::empty_like(m);
+  check_status(grmx_chunk_scan_fwd_segments(k.data_ptr(), v.data_ptr(), q.data_ptr(), m.data_ptr(), hidden.data_ptr(),
+                                            memory_out.data_ptr(), archive.data_ptr<float>(), archive.size(1),
+                                            first_slot, segment_tokens, B, T, K, H, static_cast<float>(memory_decay),
+                                            dtype_code(k.scalar_type(), "keys"), dtype_code(m.scalar_type(), "memory"),
+                                            current_stream()));
+  return {hidden, memory_out};
+}
+
 at::Tensor l2_normalize_cuda(const at::Tensor& x, double eps, bool to_bfloat16) {
   TORCH_CHECK(x.is_cuda(), "l2_normalize needs a CUDA tensor");
   TORCH_CHECK(x.dim() >= 1, "l2_normalize needs at least one dimension");
@@ -417,6 +441,7 @@ TORCH_LIBRARY(grmx, m) {
   m.def("linear_scan(Tensor keys, Tensor values, Tensor queries, Tensor memory, float decay, float update_coeff, float hidden_scale, float memory_out_scale, bool reverse, bool first_step_no_decay, int path) -> (Tensor hidden, Tensor memory_out)");
   m.def("topk_route(Tensor queries, Tensor keys, Tensor? visible, int top_k, float scale, float temperature, bool return_scores) -> (Tensor gates, Tensor indices, Tensor scores)");
   m.def("retrieve_fuse(Tensor archive, Tensor indices, Tensor? gates, Tensor queries, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
+  m.def("chunk_scan_segments(Tensor keys, Tensor values, Tensor queries, Tensor memory, float decay, Tensor(a!) archive, int first_slot, int segment_tokens) -> (Tensor hidden, Tensor memory_out)");
   m.def("l2_normalize(Tensor x, float eps, bool to_bfloat16) -> Tensor");
   m.def("archive_push(Tensor memory, Tensor(a!) archive, Tensor(b!)? shadow, int slot) -> ()");
   m.def("select_fuse(Tensor states, Tensor indices, Tensor gates, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
@@ -429,6 +454,7 @@ TORCH_LIBRARY_IMPL(grmx, CUDA, m) {
   m.impl("select_fuse", select_fuse_cuda);
   m.impl("archive_push", archive_push_cuda);
   m.impl("l2_normalize", l2_normalize_cuda);
+  m.impl("chunk_scan_segments", chunk_scan_segments_cuda);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

@@ -171,3 +171,16 @@ def normalize_rows(x, eps=1e-6, out_dtype=None):
     cabi.check(lib.grmx_normalize_rows(cabi.ptr(x), cabi.ptr(out), x.numel() // K, K, float(eps),
                                        cabi.dtype_code(x.dtype), cabi.dtype_code(out.dtype), cabi.current_stream()))
     return out
+
+
+def chunk_scan_fwd_segments(k, v, q, m, decay, archive, first_slot, segment_tokens):
+    lib = cabi.load()
+    B, T, K = k.shape
+    H = v.shape[2]
+    hidden = torch.empty_like(v)
+    m_out = torch.empty_like(m)
+    cabi.check(lib.grmx_chunk_scan_fwd_segments(cabi.ptr(k), cabi.ptr(v), cabi.ptr(q), cabi.ptr(m), cabi.ptr(hidden),
+                                                cabi.ptr(m_out), cabi.ptr(archive), archive.shape[1], first_slot,
+                                                segment_tokens, B, T, K, H, float(decay), cabi.dtype_code(k.dtype),
+                                                cabi.dtype_code(m.dtype), cabi.current_stream()))
+    return hidden, m_out

@@ -437,6 +437,39 @@ def test_select_fuse_equals_the_fused_chain_on_dense_candidates(dtype, tol, H):
 
 # --------------------------------------------------------------------------- chunk scan, tcgen05 path
 
+@pytest.mark.parametrize("B,T,L,K,H", [(2, 1024, 256, 64, 64), (8, 2048, 512, 64, 128), (64, 2048, 128, 64, 64),
+                                       (1, 4096, 512, 128, 64)])
+def test_scan_over_whole_segments_leaves_every_segment_state_in_the_archive(B, T, L, K, H):
+    """One launch over all segments (rows cut along T inside the kernel where rows are few) against one
+    call per segment with the state carried: hidden states, final state and every archived state."""
+    k, v, q, m = make_chunk(B + T + L, B, T, K, H)
+    tk, tv, tq = dev(k, torch.bfloat16), dev(v, torch.bfloat16), dev(q, torch.bfloat16)
+    n, first, capacity = T // L, 2, T // L + 3
+    archive = torch.full((B, capacity, H, K), 7.0, device=DEV)
+    hidden, m_out = gx.chunk_scan_fwd_segments(tk, tv, tq, dev(m), 0.97, archive, first, L)
+    carried = dev(m)
+    for j in range(n):
+        sl = slice(j * L, (j + 1) * L)
+        want_h, carried = gx.chunk_scan_fwd(tk[:, sl].contiguous(), tv[:, sl].contiguous(), tq[:, sl].contiguous(),
+                                            carried, 0.97, cabi.PATH_TCGEN05)
+        close(hidden[:, sl], host(want_h), LOWP_TOL)
+        close(archive[:, first + j], host(carried), LOWP_TOL)
+    close(m_out, host(carried), LOWP_TOL)
+    assert torch.equal(archive[:, first + n - 1], m_out)          # the last segment's state is the final state
+    untouched = torch.cat([archive[:, :first], archive[:, first + n:]], dim=1)
+    assert bool((untouched == 7.0).all())                          # other slots are not written
+    # against the sequential oracle as well, on the values the kernel sees
+    want = go.chunk_update_sequential(host(tk), host(tv), host(tq), m, 0.97)
+    close(hidden, want[0], LOWP_TOL)
+    close(m_out, want[1], LOWP_TOL)
+    assert cabi.device_error_word() == 0
+    lib = cabi.load()
+    rc = lib.grmx_chunk_scan_fwd_segments(cabi.ptr(tk), cabi.ptr(tv), cabi.ptr(tq), cabi.ptr(dev(m)), cabi.ptr(hidden),
+                                          cabi.ptr(m_out), cabi.ptr(archive), capacity, first, 192, B, T, K, H, 0.97,
+                                          cabi.BF16, cabi.F32, cabi.current_stream())
+    assert rc == 2 and b"128" in lib.grmx_last_error()
+
+
 def _tc_case(seed, B, T, decay, zero_state):
     k, v, q, m = make_chunk(seed, B, T, 64, 64, zero_state=zero_state)
     tk, tv, tq = dev(k, torch.bfloat16), dev(v, torch.bfloat16), dev(q, torch.bfloat16)
