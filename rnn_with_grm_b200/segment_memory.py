@@ -75,6 +75,13 @@ class SegmentMemoryArchive:
         self._route_key_buffer(route_keys.shape[-1])[:, first:first + n].copy_(route_keys)
         return True
 
+    def note_pushed(self, n: int) -> None:
+        """``n`` segments were written into the slots after the held ones (by the scan itself)."""
+        if self.head != 0 or self.count + n > self.capacity:
+            raise RuntimeError("slots written in place must not wrap or evict")
+        self.count += n
+        self.total_pushed += n
+
     def keep_bf16_copy(self) -> None:
         if self.memories_bf16 is None:
             self.memories_bf16 = self.memories.to(torch.bfloat16)
@@ -207,6 +214,9 @@ class SegmentMemoryRunner:
         # The scores are the same sums associated differently, equal to fp32 rounding.
         # Set it before the first call (the archive keeps the keys in the form they were pushed in).
         self.fold_routing_projection = True
+        # Whole segments of bf16 activations that fit the archive without evicting run as one scan
+        # launch plus one routing / selection pass for all tokens (see _run_whole_sequence).
+        self.fuse_segments = True
         self._route_query_weight: Optional[Tensor] = None
         self._fp32_cache: Dict[str, Tuple[Tensor, Tensor, int]] = {}
         self._visible_cache: Dict[Tuple[int, int, str], Tensor] = {}
@@ -316,6 +326,10 @@ class SegmentMemoryRunner:
                 return fused.to(h_online.dtype)
             contrib = torch.ops.grmx.retrieve_fuse(archive.memories, phys, gates, q_t, None, None, None, self.eps,
                                                    FUSE_CONTRIB).to(h_online.dtype)
+        return self._fuse_rule(h_online, contrib)
+
+    def _fuse_rule(self, h_online: Tensor, contrib: Tensor) -> Tensor:
+        """The fusion rules other than the plain residual one, on the gate-weighted contribution."""
         # aggregator.py:116-145
         if self.mode == "residual":
             fused = h_online + contrib
@@ -330,7 +344,8 @@ class SegmentMemoryRunner:
             fused = _linear(h_online, self.p, "aggregator.online_projection") + \
                 _linear(contrib, self.p, "aggregator.memory_projection")
         if self.use_layer_norm:
-            fused = F.layer_norm(fused, (self.hidden,), ln_w, ln_b, self.eps)
+            fused = F.layer_norm(fused, (self.hidden,), self.p.get("aggregator.layer_norm.weight"),
+                                 self.p.get("aggregator.layer_norm.bias"), self.eps)
         return fused
 
     # ---- the segment loop ------------------------------------------------------------------
@@ -341,6 +356,8 @@ class SegmentMemoryRunner:
         """``x_seq [B, T, D]`` -> ``(outputs [B, T, out], h_final [B, H], memory_final [B, H, K], aux)``."""
         B, T, _ = x_seq.shape
         L = self.segment_length
+        if self.whole_sequence_applies(x_seq, reset_memory):
+            return self._run_whole_sequence(x_seq, c_init, reset_memory, return_routes)
         if T > 0 and T % L == 0:
             x_sm = x_seq.reshape(B, T // L, L, -1).transpose(0, 1).contiguous()
             out, last_hidden, memory, aux = self._run(x_sm, True, c_init, reset_memory, return_routes)
@@ -356,6 +373,118 @@ class SegmentMemoryRunner:
         if x_sm.dim() != 4 or x_sm.shape[2] != self.segment_length:
             raise ValueError("expected [segments, B, segment_length, D]")
         return self._run(x_sm.contiguous(), True, c_init, reset_memory, return_routes)
+
+    # ---- all segments at once ------------------------------------------------------------------
+    #
+    # The retrieval of a segment never feeds back into the recurrence: the memory update reads the
+    # keys and values of the layer input only (paper_grm.py:491-523), and the fused hidden state goes
+    # to the output projection.  What is sequential in the segments is the scan state alone.  So one
+    # scan launch runs over the whole sequence and leaves the state at every segment end in the
+    # archive ring, and routing, dense apply-query and selection follow for all tokens at once: a
+    # token of segment i may choose among the first count0 + i slots only, the later slots (already
+    # written) stay invisible to it.
+
+    def whole_sequence_applies(self, x: Tensor, reset_memory: bool) -> bool:
+        L = self.segment_length
+        B, T = x.shape[0], x.shape[1]
+        if not (self.fuse_segments and x.is_cuda and x.dtype == torch.bfloat16 and T > 0 and T % L == 0 and L % 128 == 0):
+            return False
+        if self.init_mode != "checkpoint" or not self.dense_retrieval or self.capacity > 16:
+            return False
+        if self.key_dim % 64 or self.hidden % 64 or self.key_dim > 1024 or self.hidden > 1024:
+            return False
+        held = 0
+        if self.archive is not None and not reset_memory:
+            if self.archive.head != 0 or self.archive.memories.shape[0] != B:
+                return False
+            held = self.archive.count
+        return held + T // L <= self.capacity
+
+    def _run_whole_sequence(self, x: Tensor, c_init: Optional[Tensor], reset_memory: bool, return_routes: bool):
+        B, T, _ = x.shape
+        L = self.segment_length
+        n_seg = T // L
+        if reset_memory:
+            self.clear_memory()
+        if self.archive is None:
+            self.archive = SegmentMemoryArchive(B, self.capacity, self.hidden, self.key_dim, self.input_size, x.device)
+        archive = self.archive
+        archive.keep_bf16_copy()
+        memory = c_init.float() if c_init is not None else torch.zeros(B, self.hidden, self.key_dim, device=x.device,
+                                                                       dtype=torch.float32)
+        k = _l2_normalized(_linear(x, self.p, "memory_cell.key_proj"))
+        v = _linear(x, self.p, "memory_cell.value_proj")
+        q = _l2_normalized(_linear(x, self.p, "memory_cell.query_proj"))
+        summaries = x.reshape(B, n_seg, L, -1).mean(dim=2, dtype=torch.float32)
+        route_q_weight = self._fp32_param("gating_unit.query_projection.weight")
+        self._route_key_weight = self._fp32_param("gating_unit.key_projection.weight")
+        fold = self.fold_routing_projection and self.input_size <= 2 * self.route_dim
+        self._route_query_weight = route_q_weight if fold else None
+        if archive.count > 0 and archive.route_keys is None:       # an archive restored from a saved state
+            archive.set_route_keys(self._route_keys(archive.ordered_summaries()))
+        first = archive.count                                        # head == 0 here
+        if not archive.write_ahead(summaries, self._route_keys(summaries)):
+            raise RuntimeError("the archive cannot take the segments of this call without evicting")
+        hidden, memory = torch.ops.grmx.chunk_scan_segments(k, v, q, memory, self.decay, archive.memories, first, L)
+        archive.note_pushed(n_seg)
+        archive.memories_bf16[:, first:first + n_seg].copy_(archive.memories[:, first:first + n_seg])
+        held = first + n_seg
+        routes = []
+        if held > 1 or first > 0:
+            visible = self._visible_ramp(T, L, first, x.device)      # tokens of segment i see first + i slots
+            route_q = x if fold else F.linear(x.float(), route_q_weight)
+            gates, indices = self._route(route_q, archive.route_keys, visible)
+            ring = archive.memories_bf16[:, :held].reshape(B, held * self.hidden, self.key_dim)
+            ln_w = self._fp32_param("aggregator.layer_norm.weight") if self.use_layer_norm else None
+            ln_b = self._fp32_param("aggregator.layer_norm.bias") if self.use_layer_norm else None
+            plain_residual = (self.mode == "residual" and self.use_layer_norm
+                              and "aggregator.output_projection.weight" not in self.p)
+            # the candidate states of a block of segments at a time (at most ~1 GiB of them)
+            per_segment = B * L * held * self.hidden * 2
+            block = max(1, min(n_seg, (1 << 30) // max(per_segment, 1)))
+            pieces = []
+            for s0 in range(0, n_seg, block):
+                s1 = min(s0 + block, n_seg)
+                tok = slice(s0 * L, s1 * L)
+                slots = first + s1 - 1                                # the last segment of the block sees this many
+                if slots == 0:
+                    pieces.append(hidden[:, tok])
+                    continue
+                states = torch.matmul(q[:, tok], ring[:, : slots * self.hidden].transpose(1, 2)).view(
+                    B, (s1 - s0) * L, slots, self.hidden)
+                if plain_residual:
+                    pieces.append(torch.ops.grmx.select_fuse(states, indices[:, tok].contiguous(), gates[:, tok].contiguous(),
+                                                             hidden[:, tok].contiguous(), ln_w, ln_b, self.eps,
+                                                             FUSE_RESIDUAL_LN))
+                else:
+                    contrib = torch.ops.grmx.select_fuse(states, indices[:, tok].contiguous(), gates[:, tok].contiguous(),
+                                                         None, None, None, self.eps, FUSE_CONTRIB)
+                    pieces.append(self._fuse_rule(hidden[:, tok], contrib))
+            fused = pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=1)
+            if first == 0 and not plain_residual:
+                # the first segment saw an empty archive: no fusion at all for it (paper_grm.py:620-621;
+                # the plain residual kernel passes such tokens through by itself)
+                fused = torch.cat([hidden[:, :L], fused[:, L:]], dim=1)
+            if return_routes:
+                for i in range(n_seg):
+                    if first + i > 0:
+                        routes.append((gates[:, i * L:(i + 1) * L], indices[:, i * L:(i + 1) * L]))
+        else:
+            fused = hidden
+        last_hidden = fused[:, -1]
+        out = _linear(fused, self.p, "output_proj")
+        aux = {"num_segments": archive.count, "total_pushed": archive.total_pushed}
+        if return_routes:
+            aux["routes"] = routes
+        return out, last_hidden, memory, aux
+
+    def _visible_ramp(self, T: int, L: int, first: int, device) -> Tensor:
+        key = ("ramp", T, L, first, str(device))
+        t = self._visible_cache.get(key)
+        if t is None:
+            t = (torch.arange(T, device=device, dtype=torch.int32) // L + first).to(torch.int32)
+            self._visible_cache[key] = t
+        return t
 
     def _run(self, x: Tensor, segment_major: bool, c_init: Optional[Tensor], reset_memory: bool,
              return_routes: bool):
@@ -510,7 +639,10 @@ class StackedSegmentMemoryRunner:
         L = next(iter(lengths))
         # whole segments of one length in every layer: keep segment i of all batch rows contiguous from
         # the embedding to the last layer, so that no layer transposes its input or its output
-        segment_major = len(lengths) == 1 and T > 0 and T % L == 0
+        act_dtype = p["embedding.weight"].dtype if self.language_model else x.dtype
+        probe = torch.empty(B, T, 0, device=x.device, dtype=act_dtype)
+        whole = all(layer.whole_sequence_applies(probe, reset_memory) for layer in self.layers)
+        segment_major = len(lengths) == 1 and T > 0 and T % L == 0 and not whole
         if segment_major:
             x = x.reshape(B, T // L, L, *x.shape[2:]).transpose(0, 1).contiguous()
         h = F.embedding(x, p["embedding.weight"]) if self.language_model else x

@@ -205,3 +205,64 @@ def test_four_layer_language_model_bf16_activations_fp32_state(golden):
     # bf16 inputs with fp32 state
     assert go.rel_err(got, g["logits"]) < 2e-2 * 4
     assert go.rel_err(c_final.flatten(2).norm(dim=-1).cpu().numpy(), g["c_final_norm"]) < 2e-2
+
+
+def test_whole_sequence_form_equals_the_segment_loop(golden):
+    """bf16 activations and whole segments that fit the archive run as one scan launch plus one routing
+    and selection pass for all tokens; the routes must be those of the segment loop bit for bit and the
+    outputs equal to bf16 rounding.  A second call (archive half full) and the other fusion rules too."""
+    g = golden("model_cfg1")
+    params = {k[len("param::"):]: torch.from_numpy(v).to(DEV).to(torch.bfloat16) for k, v in g.items()
+              if k.startswith("param::")}
+    x = torch.from_numpy(g["x"]).to(DEV).to(torch.bfloat16)
+    def runner(fuse, **kw):
+        r = SegmentMemoryRunner(params, segment_length=128, retrieval_top_k=2, memory_capacity_segments=8,
+                                memory_decay=0.97, **kw)
+        r.fuse_segments = fuse
+        return r
+    whole, loop = runner(True), runner(False)
+    assert whole.whole_sequence_applies(x, True) and not loop.whole_sequence_applies(x, True)
+    for call, reset in enumerate([True, False]):
+        out_w, h_w, m_w, aux_w = whole.forward(x, reset_memory=reset, return_routes=True)
+        out_l, h_l, m_l, aux_l = loop.forward(x, reset_memory=reset, return_routes=True)
+        assert aux_w["num_segments"] == aux_l["num_segments"] == 4 * (call + 1)
+        assert len(aux_w["routes"]) == len(aux_l["routes"]) == (3 if call == 0 else 4)
+        for (gw, iw), (gl, il) in zip(aux_w["routes"], aux_l["routes"]):
+            assert torch.equal(iw, il) and go.rel_err(gw.cpu().numpy(), gl.cpu().numpy()) < 1e-5
+        assert go.rel_err(out_w.float().cpu().numpy(), out_l.float().cpu().numpy()) < 2e-2
+        assert go.rel_err(m_w.cpu().numpy(), m_l.cpu().numpy()) < 2e-2
+        assert go.rel_err(h_w.float().cpu().numpy(), h_l.float().cpu().numpy()) < 2e-2
+        assert torch.equal(whole.archive.memories_bf16[:, : whole.archive.count],
+                           whole.archive.memories[:, : whole.archive.count].to(torch.bfloat16))
+    # a third call would evict: the segment loop takes over
+    assert not whole.whole_sequence_applies(x, False)
+    out_w, _, _, _ = whole.forward(x, reset_memory=False)
+    out_l, _, _, _ = loop.forward(x, reset_memory=False)
+    assert go.rel_err(out_w.float().cpu().numpy(), out_l.float().cpu().numpy()) < 2e-2
+
+
+@pytest.mark.parametrize("mode", ["concat", "gate", "linear"])
+def test_whole_sequence_form_with_the_other_fusion_rules(golden, mode):
+    g = golden("model_cfg1")
+    f = golden(f"fusion_{mode}")
+    params = {k[len("param::"):]: torch.from_numpy(v).to(DEV) for k, v in g.items() if k.startswith("param::")}
+    hidden = params["memory_cell.value_proj.weight"].shape[0]
+    torch.manual_seed(0)
+    for key, value in f.items():          # same parameter names as the fixture, sized for this model
+        if not key.startswith("param::") or "layer_norm" in key:
+            continue
+        name = "aggregator." + key[len("param::"):]
+        if value.ndim == 1:
+            params[name] = torch.zeros(hidden, device=DEV)
+        else:
+            cols = 2 * hidden if value.shape[1] == 2 * value.shape[0] else hidden
+            params[name] = torch.randn(hidden, cols, device=DEV) * 0.05
+    params = {k: v.to(torch.bfloat16) for k, v in params.items()}
+    x = torch.from_numpy(g["x"]).to(DEV).to(torch.bfloat16)
+    outs = []
+    for fuse in (True, False):
+        r = SegmentMemoryRunner(params, segment_length=128, retrieval_top_k=2, memory_capacity_segments=8,
+                                memory_decay=0.97, retrieval_fusion_mode=mode)
+        r.fuse_segments = fuse
+        outs.append(r.forward(x, reset_memory=True)[0].float().cpu().numpy())
+    assert go.rel_err(outs[0], outs[1]) < 2e-2
