@@ -439,7 +439,9 @@ class SegmentMemoryRunner:
             ln_b = self._fp32_param("aggregator.layer_norm.bias") if self.use_layer_norm else None
             plain_residual = (self.mode == "residual" and self.use_layer_norm
                               and "aggregator.output_projection.weight" not in self.p)
-            # the candidate states of a block of segments at a time (at most ~1 GiB of them)
+            # the candidate states of a block of segments at a time, at most ~1 GiB of them (one block at
+            # config 4; four blocks, each with only the candidates its last segment sees, compute 40 %
+            # less but measured slower: 5.24 against 4.92 ms)
             per_segment = B * L * held * self.hidden * 2
             block = max(1, min(n_seg, (1 << 30) // max(per_segment, 1)))
             pieces = []
