@@ -110,6 +110,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // descriptor + byte offset (the start-address field holds addr >> 4 in its low 14 bits)
 __device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
 
+// kSnapshots: also write the state at segment ends (ScanParams::snapshots).  A variant of its own:
+// the test in the state group's loop costs the plain scan a tenth of its speed.
+template <bool kSnapshots>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -437,7 +440,8 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
         }
         tc_fence_before();
         mbar_arrive(&bar_u_free[c & 1]);
-        if (p.snapshots != nullptr && c >= pre && owns_row && (g0 + c + 1) % p.snap_chunks == 0) {
+        if constexpr (kSnapshots) {
+        if (c >= pre && owns_row && (g0 + c + 1) % p.snap_chunks == 0) {
           // a segment ends with this chunk: its state goes to the caller's archive
           float* snap = p.snapshots + b * p.snap_batch_stride + ((g0 + c + 1) / p.snap_chunks - 1) * p.snap_stride +
                         (x_v + state_row) * p.K + x_k;
@@ -447,6 +451,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 make_float4(m[j] * p.memory_out_scale, m[j + 1] * p.memory_out_scale, m[j + 2] * p.memory_out_scale,
                             m[j + 3] * p.memory_out_scale);
           }
+        }
         }
         if (!last) {
           if (c + 1 >= pre) {                 // the next chunk is an own chunk: [S | R] needs the state
@@ -639,8 +644,12 @@ int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaSt
   {
     std::lock_guard<std::mutex> lock(mutex);
     if (device >= 0 && device < 64 && !configured[device]) {
-      attr_status = cudaFuncSetAttribute(linear_scan_tc_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      attr_status = cudaFuncSetAttribute(linear_scan_tc_pipe_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemAlloc);
+      if (attr_status == cudaSuccess) {
+        attr_status = cudaFuncSetAttribute(linear_scan_tc_pipe_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kSmemAlloc);
+      }
       configured[device] = attr_status == cudaSuccess;
     }
   }
@@ -674,8 +683,11 @@ int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaSt
     config.attrs = attribute;
     config.numAttrs = pdl ? 1 : 0;
     const cudaError_t launched =
-        cudaLaunchKernelEx(&config, linear_scan_tc_pipe_kernel, map_q, map_k, map_v, map_o, p, split, x_k,
-                           x_k > 0 ? 1 : 0, device_error_word_ptr());
+        p.snapshots != nullptr
+            ? cudaLaunchKernelEx(&config, linear_scan_tc_pipe_kernel<true>, map_q, map_k, map_v, map_o, p, split, x_k,
+                                 x_k > 0 ? 1 : 0, device_error_word_ptr())
+            : cudaLaunchKernelEx(&config, linear_scan_tc_pipe_kernel<false>, map_q, map_k, map_v, map_o, p, split, x_k,
+                                 x_k > 0 ? 1 : 0, device_error_word_ptr());
     if (launched != cudaSuccess) {
       return fail(GRMX_ERR_LAUNCH, "linear_scan_tcgen05_pipe: launch failed: %s", cudaGetErrorString(launched));
     }
