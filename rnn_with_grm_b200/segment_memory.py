@@ -217,6 +217,7 @@ class SegmentMemoryRunner:
         # Whole segments of bf16 activations that fit the archive without evicting run as one scan
         # launch plus one routing / selection pass for all tokens (see _run_whole_sequence).
         self.fuse_segments = True
+        self.max_state_bytes = 1 << 30      # candidate states held at a time by the whole-sequence form
         self._route_query_weight: Optional[Tensor] = None
         self._fp32_cache: Dict[str, Tuple[Tensor, Tensor, int]] = {}
         self._visible_cache: Dict[Tuple[int, int, str], Tensor] = {}
@@ -443,7 +444,7 @@ class SegmentMemoryRunner:
             # config 4; four blocks, each with only the candidates its last segment sees, compute 40 %
             # less but measured slower: 5.24 against 4.92 ms)
             per_segment = B * L * held * self.hidden * 2
-            block = max(1, min(n_seg, (1 << 30) // max(per_segment, 1)))
+            block = max(1, min(n_seg, self.max_state_bytes // max(per_segment, 1)))
             pieces = []
             for s0 in range(0, n_seg, block):
                 s1 = min(s0 + block, n_seg)

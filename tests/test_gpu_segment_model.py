@@ -234,6 +234,11 @@ def test_whole_sequence_form_equals_the_segment_loop(golden):
         assert go.rel_err(h_w.float().cpu().numpy(), h_l.float().cpu().numpy()) < 2e-2
         assert torch.equal(whole.archive.memories_bf16[:, : whole.archive.count],
                            whole.archive.memories[:, : whole.archive.count].to(torch.bfloat16))
+    # candidate states in blocks of one segment instead of all at once: the same result
+    blocked = runner(True)
+    blocked.max_state_bytes = 1
+    out_b = blocked.forward(x, reset_memory=True)[0]
+    assert torch.equal(out_b, runner(True).forward(x, reset_memory=True)[0])
     # a third call would evict: the segment loop takes over
     assert not whole.whole_sequence_applies(x, False)
     out_w, _, _, _ = whole.forward(x, reset_memory=False)
