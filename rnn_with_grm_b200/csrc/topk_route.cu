@@ -98,6 +98,7 @@ __device__ __forceinline__ void select_and_gate(const float* sc, uint8_t* taken,
 // sequential fused multiply-add over d: bit-identical to the kernel below.
 constexpr int kFewKeys = 16;
 constexpr int kFewMaxD = 1024;
+constexpr int64_t kFewManyQueries = 16384;                   // from here on the grid fills every SM several times
 constexpr int kFewPad = 4;                                   // floats between staged query rows: the two halves of a warp read different banks
 
 __host__ __device__ constexpr size_t few_keys_smem_bytes(int D, int queries_per_cta) {
@@ -378,6 +379,11 @@ extern "C" int grmx_topk_route(const float* queries, const float* keys, const in
   if (S >= 1 && S <= kFewKeys && Q >= 64 && D >= 4 && D % 4 == 0 && D <= kFewMaxD && aligned && B <= 65535) {
     // measured at 8 x 512 queries of 512 features: one query per half-warp and 16 warps per CTA
     // (15.9 us against 29 us with four queries per half-warp and 4 warps, 43 us for the kernel below)
+    // many CTAs per SM: two queries per half-warp share each key load (116 against 125 us at 65536 queries)
+    if (B * Q >= kFewManyQueries) {
+      return launch_few_keys<2, 8, float>(queries, keys, visible, B, Q, S, D, top_k, scale, temperature, indices_out,
+                                          gates_out, scores_out, static_cast<cudaStream_t>(stream));
+    }
     return launch_few_keys<1, 16, float>(queries, keys, visible, B, Q, S, D, top_k, scale, temperature, indices_out, gates_out,
                                   scores_out, static_cast<cudaStream_t>(stream));
   }
@@ -403,6 +409,11 @@ extern "C" int grmx_topk_route_bf16q(const void* queries_bf16, const float* keys
     return fail(GRMX_ERR_UNSUPPORTED,
                 "%s: covers 1..%d keys, at least 64 queries per batch row, D %% 8 == 0, D <= %d, 16-byte aligned "
                 "inputs; widen the queries to float32 and call grmx_topk_route otherwise", who, kFewKeys, kFewMaxD);
+  }
+  if (B * Q >= kFewManyQueries) {
+    return launch_few_keys<2, 8, __nv_bfloat16>(static_cast<const __nv_bfloat16*>(queries_bf16), keys, visible, B, Q, S,
+                                                D, top_k, scale, temperature, indices_out, gates_out, scores_out,
+                                                static_cast<cudaStream_t>(stream));
   }
   return launch_few_keys<1, 16, __nv_bfloat16>(static_cast<const __nv_bfloat16*>(queries_bf16), keys, visible, B, Q, S,
                                                D, top_k, scale, temperature, indices_out, gates_out, scores_out,
