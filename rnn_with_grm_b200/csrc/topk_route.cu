@@ -12,6 +12,8 @@
 // visible key is selected, softmax over the selected scores only.
 #include <math_constants.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace grmx {
@@ -347,12 +349,23 @@ int launch_few_keys(const TQ* queries, const float* keys, const int32_t* visible
                     int64_t D, int top_k, float scale, float temperature, int64_t* indices_out, float* gates_out,
                     float* scores_out, cudaStream_t stream) {
   constexpr int per_cta = 2 * kChains * kWarps;
-  static const cudaError_t opted =
-      cudaFuncSetAttribute(topk_route_few_keys_kernel<kChains, kWarps, TQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(few_keys_smem_bytes(kFewMaxD, per_cta)));
-  GRMX_REQUIRE(opted == cudaSuccess, "grmx_topk_route: shared-memory opt-in failed: %s", cudaGetErrorString(opted));
+  const size_t need = few_keys_smem_bytes(static_cast<int>(D), per_cta);
+  {
+    // the opt-in is per device and grows with the largest request seen there
+    static std::mutex mutex;
+    static size_t configured[64] = {0};
+    int device = 0;
+    cudaGetDevice(&device);
+    std::lock_guard<std::mutex> lock(mutex);
+    if (device < 0 || device >= 64 || need > configured[device]) {
+      const cudaError_t opted = cudaFuncSetAttribute(topk_route_few_keys_kernel<kChains, kWarps, TQ>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(need));
+      GRMX_REQUIRE(opted == cudaSuccess, "grmx_topk_route: shared-memory opt-in failed: %s", cudaGetErrorString(opted));
+      if (device >= 0 && device < 64) configured[device] = need;
+    }
+  }
   const dim3 grid(static_cast<unsigned>((Q + per_cta - 1) / per_cta), static_cast<unsigned>(B));
-  topk_route_few_keys_kernel<kChains, kWarps, TQ><<<grid, kWarps * 32, few_keys_smem_bytes(static_cast<int>(D), per_cta), stream>>>(
+  topk_route_few_keys_kernel<kChains, kWarps, TQ><<<grid, kWarps * 32, need, stream>>>(
       queries, keys, visible, Q, static_cast<int>(S), static_cast<int>(D), top_k, scale, temperature, indices_out,
       gates_out, scores_out);
   return check_launch("topk_route_few_keys");
