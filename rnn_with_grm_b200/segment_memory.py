@@ -1,15 +1,24 @@
 """The callers on either side of the kernels: archive, segment loop, stacked model.
 
-``SegmentMemoryRunner.forward`` is the segment loop of the reference's
-``SegmentRecurrentMemoryModel.forward`` (grm/core/paper_grm.py:647-747) driven by this
-engine's kernels, with two structural changes that leave results unchanged:
+``SegmentMemoryRunner.forward`` is the reference's ``SegmentRecurrentMemoryModel.forward``
+(grm/core/paper_grm.py:647-747) driven by this engine's kernels, restructured in ways that leave the
+results unchanged:
 
-* the archive is a preallocated device ring ``[B, capacity, H, K]`` written in place at the end
-  of each segment, instead of a deque of tensors that is re-stacked and permuted for every
-  segment (paper_grm.py:135-146, 227-228);
-* gather, apply-query, gate-weighted sum, residual and LayerNorm are one kernel
-  (``torch.ops.grmx.retrieve_fuse``) that reads the selected matrices straight from the ring, so
-  the ``[B, C, R, H, K]`` tensor of paper_grm.py:229-234 never exists.
+* the archive is a preallocated device ring ``[B, capacity, H, K]`` written in place, instead of a
+  deque of tensors that is re-stacked and permuted for every segment (paper_grm.py:135-146, 227-228);
+  it also keeps the routing keys of its segments (projected once) and, for bf16 activations, a bf16
+  copy of the ring;
+* retrieval never materialises the gathered ``[B, C, R, H, K]`` tensor of paper_grm.py:229-234:
+  either one kernel reads the selected matrices straight from the ring
+  (``torch.ops.grmx.retrieve_fuse``), or, with per-token routing, the queries of a segment are
+  applied to all archived matrices with one batched GEMM and ``torch.ops.grmx.select_fuse`` picks,
+  weights, adds and normalises;
+* everything that depends on the layer input alone (projections, summaries, routing keys) is
+  computed for the whole sequence before the loop;
+* bf16 activations over whole segments that fit the archive run without a loop at all: one scan
+  launch leaves the state at every segment end in the ring, then routing, apply-query and selection
+  run once for all tokens (``_run_whole_sequence``); the retrieval of a segment never feeds back into
+  the recurrence, and a token of segment i sees only the slots that were archived before it.
 
 Parameters are taken by the names of the reference model's ``state_dict`` so a checkpoint of
 the reference loads as is.  Projections and the weight-bearing fusion rules are plain
