@@ -656,6 +656,8 @@ def main(argv=None) -> int:
                         help="time the two-kernel variant of the cut (piece-state kernel + scan over a caller workspace)")
     parser.add_argument("--full-occupancy-only", action="store_true",
                         help="run only the one-row-per-SM scan of the extras and print its figures (for profiling)")
+    parser.add_argument("--config4-only", action="store_true",
+                        help="run only the config-4 language-model forward of the extras (for profiling)")
     parser.add_argument("--segment-retrieval-only", action="store_true",
                         help="run only the per-token routing and select-fuse kernels of one config-4 segment (for profiling)")
     args = parser.parse_args(argv)
@@ -683,6 +685,12 @@ def main(argv=None) -> int:
     if args.full_occupancy_only:
         from rnn_with_grm_b200 import cabi
         print(json.dumps({"full_occupancy_scan": full_occupancy_scan(cabi.load(), device, load_peaks()[0])}), flush=True)
+        return 0
+    if args.config4_only:
+        from rnn_with_grm_b200 import cuda_ops
+        if not cuda_ops.load_grm_cuda_extension():
+            raise RuntimeError("grm_cuda extension failed to load: " + cuda_ops.get_grm_cuda_runtime_status()["load_error"])
+        print(json.dumps({"cfg4_model": config4_model(device)}), flush=True)
         return 0
     if args.segment_retrieval_only:
         from rnn_with_grm_b200 import cabi
