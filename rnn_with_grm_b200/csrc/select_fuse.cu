@@ -210,12 +210,32 @@ select_fuse_kernel(const T* __restrict__ states, const int64_t* __restrict__ ind
   for (int i = 0; i < kPieces; ++i) {
     const int h = (lane + 32 * i) * VEC;
     if (h < H) {
+      // weight and bias of the piece in 16-byte loads (one 4-byte load per element costs the cache a
+      // line per lane and instruction: a thousand wavefronts per row of 512)
+      float wv[VEC], bv[VEC];
+      if constexpr (VEC % 4 == 0) {
+#pragma unroll
+        for (int j4 = 0; j4 < VEC / 4; ++j4) {
+          const float4 w4 = ln_weight != nullptr ? __ldg(reinterpret_cast<const float4*>(ln_weight + h) + j4)
+                                                 : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+          const float4 b4 = ln_bias != nullptr ? __ldg(reinterpret_cast<const float4*>(ln_bias + h) + j4)
+                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          wv[4 * j4] = w4.x; wv[4 * j4 + 1] = w4.y; wv[4 * j4 + 2] = w4.z; wv[4 * j4 + 3] = w4.w;
+          bv[4 * j4] = b4.x; bv[4 * j4 + 1] = b4.y; bv[4 * j4 + 2] = b4.z; bv[4 * j4 + 3] = b4.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+          wv[j] = ln_weight != nullptr ? __ldg(ln_weight + h + j) : 1.0f;
+          bv[j] = ln_bias != nullptr ? __ldg(ln_bias + h + j) : 0.0f;
+        }
+      }
       float y[VEC];
 #pragma unroll
       for (int j = 0; j < VEC; ++j) {
         y[j] = (x[i][j] - mean) * rstd;
-        if (ln_weight != nullptr) y[j] *= __ldg(ln_weight + h + j);
-        if (ln_bias != nullptr) y[j] += __ldg(ln_bias + h + j);
+        if (ln_weight != nullptr) y[j] *= wv[j];
+        if (ln_bias != nullptr) y[j] += bv[j];
       }
       store_piece<T, VEC>(out + bq * H + h, y);
     }
@@ -276,7 +296,8 @@ extern "C" int grmx_select_fuse(const void* states, const int64_t* indices, cons
   uint32_t* err = device_error_word_ptr();
   // 16-byte pieces when every row starts on a 16-byte boundary
   const uintptr_t bases = reinterpret_cast<uintptr_t>(states) | reinterpret_cast<uintptr_t>(online) |
-                          reinterpret_cast<uintptr_t>(out);
+                          reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(ln_weight) |
+                          reinterpret_cast<uintptr_t>(ln_bias);
   const int per16 = dtype == GRMX_F32 ? 4 : 8;
   const bool vec = H % per16 == 0 && (bases & 15u) == 0;
   if (dtype == GRMX_F32) {
