@@ -136,18 +136,28 @@ int grmx_chunk_scan_fwd_ws(const void* keys, const void* values, const void* que
 /*
  * The same scan for callers that cannot allocate device memory where they call it (a server
  * that has given all of HBM to its own pool, a real-time callback, a sandboxed plugin that
- * only owns its input and output buffers).  bf16 tokens, fp32 state, d_k = d_v = 64, layouts
- * as in grmx_chunk_scan_fwd.  The workspace is an array inside the library image,
+ * only owns its input and output buffers).  bf16 tokens, fp32 state, d_k and d_v multiples of 64,
+ * layouts as in grmx_chunk_scan_fwd.  The workspace is an array inside the library image,
  * grmx_static_scratch_capacity() bytes (4 MiB) of device memory held by every GPU that loads
- * the library until the process exits; a call that would need more is refused with
- * GRMX_ERR_UNSUPPORTED, and nothing is ever allocated or freed.  The first call on each device
- * looks the array's address up (cudaGetSymbolAddress, with that device current), so make that
- * first call outside any stream capture.  All calls share the one array: nothing in it has to
- * be cleared between calls (each call overwrites what it later reads), but two calls that run
- * on the GPU at the same time -- different streams, or different host threads -- race on it.
+ * the library until the process exits; only heads of 64 x 64 are ever cut over it (wider heads
+ * run the one-launch form and do not touch the array).  A call that would need more than the
+ * array holds is refused with GRMX_ERR_UNSUPPORTED, and nothing is ever allocated or freed.
+ * The first call on each device looks the array's address up (cudaGetSymbolAddress, with that
+ * device current), so make that first call outside any stream capture; the remembered address
+ * does not survive cudaDeviceReset or the teardown of the device's primary context.  All calls
+ * share the one array: nothing in it has to be cleared between calls (each call overwrites what
+ * it later reads), but two calls that run on the GPU at the same time -- different streams, or
+ * different host threads -- race on it.
+ * grmx_chunk_scan_scratch_bytes_on is grmx_chunk_scan_scratch_bytes for a device of sm_count
+ * multiprocessors instead of the current one (a pure host computation), and
+ * grmx_static_scratch_admits(need) is the admission test itself: GRMX_OK when `need` bytes fit the
+ * array, GRMX_ERR_UNSUPPORTED with the refusal text otherwise.  Together they tell a caller ahead
+ * of time, without a GPU, whether a shape will be accepted.
  * No counterpart in the reference.
  */
 int64_t grmx_static_scratch_capacity(void);
+int64_t grmx_chunk_scan_scratch_bytes_on(int64_t B, int64_t T, int64_t K, int64_t H, int sm_count);
+int grmx_static_scratch_admits(int64_t need_bytes);
 int grmx_chunk_scan_fwd_static(const void* keys, const void* values, const void* queries,
                                const void* memory_in, void* hidden_out, void* memory_out,
                                int64_t B, int64_t T, int64_t K, int64_t H, float decay,

@@ -2,7 +2,9 @@
 
 ``c_oracle()`` returns the ctypes handle of the plain-C restatement,
 ``reference_ops()`` the ``torch.ops.grm_ref`` namespace served by the
-reference's own compiled CPU code, or ``None`` when that library was not built.
+reference's own compiled CPU code, or ``None`` when that library was not built,
+``reference_python()`` the folder that holds the staged reference package ``grm``
+(to be put on ``sys.path``), or ``None`` when it was not staged.
 """
 
 from __future__ import annotations
@@ -55,6 +57,12 @@ def reference_ops():
         torch.ops.load_library(str(path))
         _REF_LOADED = True
     return torch.ops.grm_ref
+
+
+def reference_python():
+    """Folder holding the staged reference package (``oracle/_ref/python``) or ``None``."""
+    path = _HERE / "_ref" / "python"
+    return path if (path / "grm" / "__init__.py").exists() else None
 
 
 # ---- numpy-facing wrappers of the C functions ----

@@ -34,7 +34,7 @@ CUDA_SOURCES = [
     "cabi.cu",
     "chunk_scan.cu",
     "chunk_scan_ffma.cu",
-    "chunk_scan_tc.cu",
+    "tc_host.cu",
     "chunk_scan_tc_pipe.cu",
     "chunk_scan_tc_split.cu",
     "apply_query.cu",

@@ -48,6 +48,8 @@ SIGNATURES = {
         [c_void_p] * 6 + [c_int64] * 4 + [c_float, c_int, c_int, c_int, c_void_p, c_int64, c_void_p],
     ),
     "grmx_static_scratch_capacity": (c_int64, []),
+    "grmx_chunk_scan_scratch_bytes_on": (c_int64, [c_int64] * 4 + [c_int]),
+    "grmx_static_scratch_admits": (c_int, [c_int64]),
     "grmx_chunk_scan_fwd_static": (c_int, [c_void_p] * 6 + [c_int64] * 4 + [c_float, c_void_p]),
     "grmx_chunk_scan_bwd": (
         c_int,

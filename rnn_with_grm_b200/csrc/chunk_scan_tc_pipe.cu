@@ -107,6 +107,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// 16-byte load through the coherent path (ld.global, never ld.global.nc)
+__device__ __forceinline__ float4 ld_coherent_f4(const float4* ptr) {
+  float4 v;
+  asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(ptr) : "memory");
+  return v;
+}
+
 // descriptor + byte offset (the start-address field holds addr >> 4 in its low 14 bits)
 __device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
 
@@ -375,10 +382,13 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
       const float* m_in = static_cast<const float*>(p.memory_in) + b * p.H * p.K;
       const float* src = m_in + (x_v + state_row) * p.m_row_stride + x_k * p.m_col_stride;
       const bool vec = p.m_col_stride == 1 && (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+      // Plain (coherent) loads: as a programmatic dependent this grid is alive while the grid before it
+      // still writes memory_in (a state carried from call to call) and the piece states, so the
+      // read-only data path, which assumes the data never changes during the kernel, is not used.
       if (owns_row && vec) {
 #pragma unroll
         for (int j = 0; j < kD / 4; ++j) {
-          const float4 x = __ldg(reinterpret_cast<const float4*>(src) + j);
+          const float4 x = ld_coherent_f4(reinterpret_cast<const float4*>(src) + j);
           m[4 * j] = x.x; m[4 * j + 1] = x.y; m[4 * j + 2] = x.z; m[4 * j + 3] = x.w;
         }
       } else {
@@ -397,7 +407,7 @@ linear_scan_tc_pipe_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
                 split.partials + (((b * (split.pieces - 1) + q) * split.subs + sub) * kD + state_row) * kD);
 #pragma unroll
             for (int j = 0; j < kD / 4; ++j) {
-              const float4 x = __ldg(part + j);
+              const float4 x = ld_coherent_f4(part + j);
               m[4 * j] += x.x;
               m[4 * j + 1] += x.y;
               m[4 * j + 2] += x.z;

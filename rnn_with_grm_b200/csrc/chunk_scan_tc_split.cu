@@ -213,10 +213,9 @@ int sm_count_of_current_device() {
 
 // Pieces per row: the largest power of two that still gives every piece two chunks or more and
 // keeps rows x pieces within one wave of the GPU (one CTA per SM).
-int pick_pieces(const ScanParams& p) {
+int pick_pieces(const ScanParams& p, int sms) {
   if (!scan_tcgen05_pipe_supported(p)) return 1;
   const int64_t n_chunks = (p.T + kChunk - 1) / kChunk;
-  const int sms = sm_count_of_current_device();
   const int64_t ctas_per_piece = p.B * (p.H / kD);     // one CTA per row and 64-wide block of value features
   int pieces = 1;
   while (ctas_per_piece * pieces * 2 <= sms && n_chunks / (pieces * 2) >= 2) pieces *= 2;
@@ -225,32 +224,33 @@ int pick_pieces(const ScanParams& p) {
 
 // Terms per piece state: the largest power of two that keeps the piece-state kernel within one
 // wave and gives every term two chunks or more.
-int pick_subs(const ScanParams& p, int pieces, int chunks_per_piece) {
-  const int sms = sm_count_of_current_device();
+int pick_subs(const ScanParams& p, int pieces, int chunks_per_piece, int sms) {
   int subs = 1;
   while (p.B * (pieces - 1) * subs * 2 <= sms && chunks_per_piece / (subs * 2) >= 2) subs *= 2;
   return subs;
 }
 
-// the cut for this call: pieces == 1 when a cut does not apply
-SplitInfo plan_split(const ScanParams& p) {
+// the cut for this call on a device of `sms` multiprocessors (0: the current device); pieces == 1 when
+// a cut does not apply
+SplitInfo plan_split(const ScanParams& p, int sms = 0) {
+  if (sms <= 0) sms = sm_count_of_current_device();
   const int64_t n_chunks = (p.T + kChunk - 1) / kChunk;
   SplitInfo split{1, static_cast<int>(n_chunks), nullptr, 1};
-  const int pieces = pick_pieces(p);
+  const int pieces = pick_pieces(p, sms);
   if (pieces <= 1) return split;
   const int per_piece = static_cast<int>((n_chunks + pieces - 1) / pieces);
   if (static_cast<int64_t>(per_piece) * (pieces - 1) >= n_chunks) return split;   // every piece must own a chunk
   split.pieces = pieces;
   split.chunks_per_piece = per_piece;
-  split.subs = pick_subs(p, pieces, per_piece);
+  split.subs = pick_subs(p, pieces, per_piece, sms);
   return split;
 }
 
 }  // namespace
 
-int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p) {
+int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p, int sms) {
   if (p.K != kD || p.H != kD) return 0;                // the two-kernel cut exists for 64 x 64 heads only
-  const SplitInfo split = plan_split(p);
+  const SplitInfo split = plan_split(p, sms);
   if (split.pieces <= 1) return 0;
   return p.B * (split.pieces - 1) * split.subs * kD * kD * static_cast<int64_t>(sizeof(float));
 }
@@ -388,10 +388,33 @@ int static_scratch_address(float** out) {
   return GRMX_OK;
 }
 
+// The one comparison that decides whether a call fits the built-in workspace.
+int static_scratch_admit(int64_t need_bytes, const char* who) {
+  if (need_bytes > kStaticScratchBytes) {
+    return fail(GRMX_ERR_UNSUPPORTED,
+                "%s: this call needs %lld bytes of workspace, the built-in one holds %lld; use "
+                "grmx_chunk_scan_fwd_ws with a buffer of your own or fewer rows per call",
+                who, (long long)need_bytes, (long long)kStaticScratchBytes);
+  }
+  return GRMX_OK;
+}
+
 }  // namespace
 }  // namespace grmx
 
 extern "C" int64_t grmx_static_scratch_capacity(void) { return grmx::kStaticScratchBytes; }
+
+extern "C" int grmx_static_scratch_admits(int64_t need_bytes) {
+  if (need_bytes < 0) return grmx::fail(GRMX_ERR_ARG, "grmx_static_scratch_admits: negative size");
+  return grmx::static_scratch_admit(need_bytes, "grmx_static_scratch_admits");
+}
+
+extern "C" int64_t grmx_chunk_scan_scratch_bytes_on(int64_t B, int64_t T, int64_t K, int64_t H, int sm_count) {
+  if (B <= 0 || T <= 0 || K <= 0 || H <= 0 || sm_count <= 0) return 0;
+  grmx::ScanParams p = {};
+  p.B = B; p.T = T; p.K = K; p.H = H;
+  return grmx::scan_tcgen05_split_scratch_bytes(p, sm_count);
+}
 
 extern "C" int grmx_chunk_scan_fwd_static(const void* keys, const void* values, const void* queries,
                                           const void* memory_in, void* hidden_out, void* memory_out,
@@ -414,15 +437,10 @@ extern "C" int grmx_chunk_scan_fwd_static(const void* keys, const void* values, 
   if (!scan_tcgen05_supported(p, GRMX_BF16, GRMX_F32, &why)) {
     return fail(GRMX_ERR_UNSUPPORTED, "%s: only the bf16 tensor-core scan is offered here: %s", who, why);
   }
-  const int64_t need = scan_tcgen05_split_scratch_bytes(p);
-  if (need > kStaticScratchBytes) {
-    return fail(GRMX_ERR_UNSUPPORTED,
-                "%s: this call needs %lld bytes of workspace, the built-in one holds %lld; use "
-                "grmx_chunk_scan_fwd_ws with a buffer of your own or fewer rows per call",
-                who, (long long)need, (long long)kStaticScratchBytes);
-  }
+  int rc = static_scratch_admit(scan_tcgen05_split_scratch_bytes(p), who);
+  if (rc != GRMX_OK) return rc;
   float* scratch = nullptr;
-  const int rc = static_scratch_address(&scratch);
+  rc = static_scratch_address(&scratch);
   if (rc != GRMX_OK) return rc;
   return launch_scan_tcgen05_split(p, scratch, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
 }

@@ -58,7 +58,7 @@ int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaSt
 
 // Cutting along T: bytes of scratch the cut needs for this call (0 when a cut would not help or
 // the shape is not covered), and the launch that runs the piece-state kernel followed by the scan.
-int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p);
+int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p, int sm_count = 0);   // 0: the current device
 int launch_scan_tcgen05_split(const ScanParams& p, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
 // The same cut without a workspace: one launch, every piece derives its start state itself with a
 // pre-pass over the chunks before its own (state recurrence only).  Falls back to the uncut scan

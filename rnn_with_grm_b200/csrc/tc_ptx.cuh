@@ -347,7 +347,7 @@ __device__ __forceinline__ void scaled_row_copy(const uint8_t* src_tile, uint8_t
   }
 }
 
-// ---- host helpers (defined in chunk_scan_tc.cu) ----
+// ---- host helpers (defined in tc_host.cu) ----
 // cuTensorMapEncodeTiled resolved through the runtime, so the library has no link-time
 // dependency on libcuda; nullptr when the driver does not provide it.
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

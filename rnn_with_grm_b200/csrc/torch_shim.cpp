@@ -468,4 +468,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     g_scan_path.store(path);
   });
   m.def("get_scan_path", []() { return g_scan_path.load(); });
+  // The device error word of the current device: kernels report a bounded wait that gave up or an
+  // out-of-range routing index there instead of trapping.  Reading it waits for the current stream.
+  m.def("device_error_word", []() {
+    uint32_t word = 0;
+    check_status(grmx_device_error_word(&word, current_stream()));
+    return word;
+  });
+  m.def("device_error_reset", []() { check_status(grmx_device_error_reset(current_stream())); });
 }

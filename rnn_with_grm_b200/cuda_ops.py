@@ -28,142 +28,148 @@ from typing import Any, Dict, Optional, Tuple
 import torch
 from torch import Tensor
 
-_IMPORT_CANDIDATES = ("rnn_with_grm_b200.grm_cuda_ext", "grm_cuda_ext", "grm.grm_cuda_ext")
-_REGISTERED_OPS = (
+_OP_NAMES = (
     "chunk_update_forward",
     "chunk_update_backward",
     "apply_query_forward",
     "apply_query_backward",
     "batched_memory_gather",
 )
-
-_EXTENSION_MODULE: Optional[Any] = None
-_EXTENSION_LOAD_ATTEMPTED = False
-_EXTENSION_LOAD_ERROR = ""
-_KERNEL_POLICY_ENV = "GRM_CUDA_KERNEL_POLICY"
-_KERNEL_POLICY_OP_ENVS = {
-    "chunk_update": "GRM_CUDA_CHUNK_UPDATE_POLICY",
-    "apply_query": "GRM_CUDA_APPLY_QUERY_POLICY",
-    "batched_memory_gather": "GRM_CUDA_BATCHED_GATHER_POLICY",
-}
-_VALID_KERNEL_POLICIES = {"auto", "native", "fallback"}
 _SCAN_PATHS = {"auto": 0, "ffma": 1, "tcgen05": 2}
+_POLICY_VALUES = ("auto", "native", "fallback")
+# policy slot -> environment variables consulted, most specific first (reference :26-32)
+_POLICY_ENV = {
+    "global": ("GRM_CUDA_KERNEL_POLICY",),
+    "chunk_update": ("GRM_CUDA_CHUNK_UPDATE_POLICY", "GRM_CUDA_KERNEL_POLICY"),
+    "apply_query": ("GRM_CUDA_APPLY_QUERY_POLICY", "GRM_CUDA_KERNEL_POLICY"),
+    "batched_memory_gather": ("GRM_CUDA_BATCHED_GATHER_POLICY", "GRM_CUDA_KERNEL_POLICY"),
+}
+_ERROR_BITS = {
+    1: "an index outside the archive reached a gather or retrieval kernel (the row was zero-filled)",
+    2: "a bounded wait inside a tensor-core kernel gave up (outputs of that call are incomplete)",
+}
 
 
-def _has_registered_ops() -> bool:
-    namespace = getattr(torch.ops, "grm_cuda", None)
-    if namespace is None:
-        return False
-    return all(hasattr(namespace, op_name) for op_name in _REGISTERED_OPS)
+class _Extension:
+    """The one import attempt of the compiled module, remembered for the process."""
+
+    candidates = ("rnn_with_grm_b200.grm_cuda_ext", "grm_cuda_ext", "grm.grm_cuda_ext")
+    module: Optional[Any] = None
+    tried = False
+    error = ""
+
+    @classmethod
+    def ops_registered(cls) -> Dict[str, bool]:
+        namespace = getattr(torch.ops, "grm_cuda", None)
+        return {name: namespace is not None and hasattr(namespace, name) for name in _OP_NAMES}
+
+    @classmethod
+    def load(cls, force: bool) -> bool:
+        if not force and (cls.module is not None or cls.tried):
+            return cls.module is not None
+        cls.tried, cls.module, problems = True, None, []
+        for name in cls.candidates:
+            try:
+                module = importlib.import_module(name)
+            except Exception as exc:  # ImportError, OSError from the loader, ...
+                problems.append(f"{name}: {type(exc).__name__}: {exc}")
+                continue
+            if all(cls.ops_registered().values()):
+                cls.module = module
+                break
+            problems.append(f"{name}: torch.ops.grm_cuda registration missing")
+        cls.error = "" if cls.module is not None else "; ".join(problems)
+        if cls.module is not None:
+            wanted = os.environ.get("GRMX_SCAN_PATH", "").strip().lower()
+            if wanted in _SCAN_PATHS and hasattr(cls.module, "set_scan_path"):
+                cls.module.set_scan_path(_SCAN_PATHS[wanted])
+        return cls.module is not None
 
 
-def _has_dispatch_kernel(op_name: str, dispatch_key: str) -> bool:
-    checker = getattr(torch._C, "_dispatch_has_kernel_for_dispatch_key", None)
-    if checker is None:
-        return False
-    try:
-        return bool(checker(f"grm_cuda::{op_name}", dispatch_key))
-    except Exception:
-        return False
+def _dispatch_table() -> Dict[str, Dict[str, bool]]:
+    """Which dispatch keys hold a kernel for each op (reference :42-59)."""
+    probe = getattr(torch._C, "_dispatch_has_kernel_for_dispatch_key", None)
 
-
-def _get_dispatch_kernel_status() -> Dict[str, Dict[str, bool]]:
-    return {
-        op_name: {
-            "cuda": _has_dispatch_kernel(op_name, "CUDA"),
-            "composite_explicit_autograd": _has_dispatch_kernel(op_name, "CompositeExplicitAutograd"),
-        }
-        for op_name in _REGISTERED_OPS
-    }
-
-
-def load_grm_cuda_extension(force: bool = False) -> bool:
-    """Import the compiled extension once per process (reference :62-89)."""
-    global _EXTENSION_MODULE, _EXTENSION_LOAD_ATTEMPTED, _EXTENSION_LOAD_ERROR
-
-    if _EXTENSION_MODULE is not None and not force:
-        return True
-    if _EXTENSION_LOAD_ATTEMPTED and not force:
-        return False
-
-    _EXTENSION_LOAD_ATTEMPTED = True
-    _EXTENSION_MODULE = None
-    _EXTENSION_LOAD_ERROR = ""
-
-    errors = []
-    for module_name in _IMPORT_CANDIDATES:
+    def has(op: str, key: str) -> bool:
         try:
-            module = importlib.import_module(module_name)
-        except Exception as exc:
-            errors.append(f"{module_name}: {type(exc).__name__}: {exc}")
-            continue
-        if not _has_registered_ops():
-            errors.append(f"{module_name}: torch.ops.grm_cuda registration missing")
-            continue
-        _EXTENSION_MODULE = module
-        scan_path = os.environ.get("GRMX_SCAN_PATH", "").strip().lower()
-        if scan_path in _SCAN_PATHS and hasattr(module, "set_scan_path"):
-            module.set_scan_path(_SCAN_PATHS[scan_path])
-        return True
+            return probe is not None and bool(probe(f"grm_cuda::{op}", key))
+        except Exception:
+            return False
 
-    _EXTENSION_LOAD_ERROR = "; ".join(errors)
-    return False
+    return {op: {"cuda": has(op, "CUDA"), "composite_explicit_autograd": has(op, "CompositeExplicitAutograd")}
+            for op in _OP_NAMES}
 
 
-def is_grm_cpp_extension_available() -> bool:
-    return load_grm_cuda_extension()
-
-
-def _get_kernel_policy(op_name: str) -> str:
-    env_names = (_KERNEL_POLICY_OP_ENVS.get(op_name, ""), _KERNEL_POLICY_ENV)
-    for env_name in env_names:
-        if not env_name:
-            continue
-        value = os.environ.get(env_name, "").strip().lower()
-        if value in _VALID_KERNEL_POLICIES:
+def _policy(slot: str) -> str:
+    for variable in _POLICY_ENV[slot]:
+        value = os.environ.get(variable, "").strip().lower()
+        if value in _POLICY_VALUES:
             return value
     return "auto"
 
 
+def load_grm_cuda_extension(force: bool = False) -> bool:
+    """Import the compiled extension once per process (reference :62-89)."""
+    return _Extension.load(force)
+
+
+def is_grm_cpp_extension_available() -> bool:
+    return _Extension.load(False)
+
+
 def is_grm_cuda_available() -> bool:
-    if not load_grm_cuda_extension():
+    if not (_Extension.load(False) and torch.cuda.is_available()):
         return False
-    dispatch_status = _get_dispatch_kernel_status()
-    return all(status["cuda"] for status in dispatch_status.values()) and torch.cuda.is_available()
+    return all(entry["cuda"] for entry in _dispatch_table().values())
 
 
 def get_grm_cuda_runtime_status() -> Dict[str, Any]:
     """Field-for-field the dict of the reference (grm/core/cuda_ops.py:198-215)."""
-    extension_loaded = load_grm_cuda_extension()
-    namespace = getattr(torch.ops, "grm_cuda", None)
-    registered_ops = {op_name: bool(namespace and hasattr(namespace, op_name)) for op_name in _REGISTERED_OPS}
-    compiled_with_cuda_sources = bool(
-        getattr(_EXTENSION_MODULE, "__grm_cuda_with_kernels__", False) if _EXTENSION_MODULE is not None else False
-    )
-    dispatch_kernels = _get_dispatch_kernel_status() if extension_loaded else {
-        op_name: {"cuda": False, "composite_explicit_autograd": False} for op_name in _REGISTERED_OPS
-    }
-    compiled_with_cuda_kernels = compiled_with_cuda_sources and all(
-        dispatch_status["cuda"] for dispatch_status in dispatch_kernels.values()
-    )
+    loaded = _Extension.load(False)
+    module = _Extension.module
+    dispatch = _dispatch_table()
+    if not loaded:
+        dispatch = {op: dict.fromkeys(entry, False) for op, entry in dispatch.items()}
+    with_sources = bool(getattr(module, "__grm_cuda_with_kernels__", False))
+    with_kernels = with_sources and all(entry["cuda"] for entry in dispatch.values())
+    gpu = torch.cuda.is_available()
     return {
-        "load_attempted": _EXTENSION_LOAD_ATTEMPTED,
-        "extension_loaded": extension_loaded,
-        "compiled_with_cuda_sources": compiled_with_cuda_sources,
-        "compiled_with_cuda_kernels": compiled_with_cuda_kernels,
-        "torch_cuda_available": torch.cuda.is_available(),
-        "cuda_backend_available": compiled_with_cuda_kernels and torch.cuda.is_available(),
-        "load_error": _EXTENSION_LOAD_ERROR,
-        "module_name": getattr(_EXTENSION_MODULE, "__name__", "") if _EXTENSION_MODULE is not None else "",
-        "registered_ops": registered_ops,
-        "dispatch_kernels": dispatch_kernels,
-        "kernel_policy": {
-            "global": _get_kernel_policy(""),
-            "chunk_update": _get_kernel_policy("chunk_update"),
-            "apply_query": _get_kernel_policy("apply_query"),
-            "batched_memory_gather": _get_kernel_policy("batched_memory_gather"),
-        },
+        "load_attempted": _Extension.tried,
+        "extension_loaded": loaded,
+        "compiled_with_cuda_sources": with_sources,
+        "compiled_with_cuda_kernels": with_kernels,
+        "torch_cuda_available": gpu,
+        "cuda_backend_available": with_kernels and gpu,
+        "load_error": _Extension.error,
+        "module_name": getattr(module, "__name__", "") if module is not None else "",
+        "registered_ops": _Extension.ops_registered(),
+        "dispatch_kernels": dispatch,
+        "kernel_policy": {slot: _policy(slot) for slot in _POLICY_ENV},
     }
+
+
+def check_device_errors(reset: bool = True) -> None:
+    """Raise ``RuntimeError`` if a kernel of this engine reported a failure it could not raise itself.
+
+    Kernels never trap: a bounded wait that gives up, or a routing index outside the archive, sets a
+    bit in a per-device error word and the launch still returns success, so the outputs of that call
+    may be incomplete.  This reads the word of the current device (which waits for the current stream)
+    and raises if it is non-zero.  Call it wherever a synchronisation is acceptable -- after a forward
+    pass, before a checkpoint -- or set ``GRMX_CHECK_ERRORS=1`` to have every op of this module and the
+    segment runners check after each call (a debugging mode: it serialises host and device).
+    """
+    _require_extension("check_device_errors")
+    word = int(_Extension.module.device_error_word())
+    if word == 0:
+        return
+    if reset:
+        _Extension.module.device_error_reset()
+    reasons = [text for bit, text in _ERROR_BITS.items() if word & bit] or [f"unknown bits {word:#x}"]
+    raise RuntimeError(f"grm_cuda: device error word {word:#x}: " + "; ".join(reasons))
+
+
+def _checking_each_call() -> bool:
+    return os.environ.get("GRMX_CHECK_ERRORS", "").strip().lower() in ("1", "true", "on", "yes")
 
 
 def set_scan_path(path: str) -> None:
@@ -171,22 +177,22 @@ def set_scan_path(path: str) -> None:
     if path not in _SCAN_PATHS:
         raise ValueError(f"scan path must be one of {sorted(_SCAN_PATHS)}, got {path!r}")
     _require_extension("set_scan_path")
-    _EXTENSION_MODULE.set_scan_path(_SCAN_PATHS[path])
+    _Extension.module.set_scan_path(_SCAN_PATHS[path])
 
 
 def _require_extension(op_name: str) -> None:
-    if not load_grm_cuda_extension():
+    if not _Extension.load(False):
         raise RuntimeError(
-            f"{op_name}: the grm_cuda extension is not loaded ({_EXTENSION_LOAD_ERROR or 'not built'}). "
+            f"{op_name}: the grm_cuda extension is not loaded ({_Extension.error or 'not built'}). "
             "Build it with `python -m rnn_with_grm_b200.build`; this engine has no fallback path."
         )
 
 
 def _require_native(op_name: str, policy_key: str, device: torch.device, *, enabled: bool, debug_fallback: bool) -> None:
-    if not enabled or debug_fallback or _get_kernel_policy(policy_key) == "fallback":
+    if not enabled or debug_fallback or _policy(policy_key) == "fallback":
         raise RuntimeError(
             f"{op_name}: a fallback path was requested (enabled={enabled}, debug_fallback={debug_fallback}, "
-            f"policy={_get_kernel_policy(policy_key)!r}) but this engine ships only the sm_100a kernels."
+            f"policy={_policy(policy_key)!r}) but this engine ships only the sm_100a kernels."
         )
     _require_extension(op_name)
     if device.type != "cuda":
@@ -258,7 +264,10 @@ def cuda_chunk_update(
 ) -> Tuple[Tensor, Tensor]:
     """``hidden[B,T,H], memory_out[B,H,K]`` of the decayed linear-memory scan (reference :347-367)."""
     _require_native("cuda_chunk_update", "chunk_update", memory.device, enabled=enabled, debug_fallback=debug_fallback)
-    return ChunkUpdateCudaFn.apply(keys, values, queries, memory, float(memory_decay))
+    out = ChunkUpdateCudaFn.apply(keys, values, queries, memory, float(memory_decay))
+    if _checking_each_call():
+        check_device_errors()
+    return out
 
 
 def cuda_apply_query(
@@ -272,7 +281,10 @@ def cuda_apply_query(
     _require_native("cuda_apply_query", "apply_query", memories.device, enabled=enabled, debug_fallback=debug_fallback)
     if memories.ndim not in (4, 5):
         raise ValueError(f"Unsupported memory rank for apply-query: {memories.ndim}")
-    return ApplyQueryCudaFn.apply(memories, queries)
+    out = ApplyQueryCudaFn.apply(memories, queries)
+    if _checking_each_call():
+        check_device_errors()
+    return out
 
 
 def cuda_batched_memory_gather(
@@ -294,7 +306,10 @@ def cuda_batched_memory_gather(
         raise ValueError(f"Expected memories_per_batch rank 4, got {memories_per_batch.ndim}")
     if topk_indices.ndim not in {2, 3}:
         raise ValueError(f"Expected topk_indices rank 2 or 3, got {topk_indices.ndim}")
-    return torch.ops.grm_cuda.batched_memory_gather(memories_per_batch, topk_indices)
+    out = torch.ops.grm_cuda.batched_memory_gather(memories_per_batch, topk_indices)
+    if _checking_each_call():
+        check_device_errors()
+    return out
 
 
 def install_as_grm_cuda_ops() -> None:

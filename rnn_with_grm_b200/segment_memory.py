@@ -179,6 +179,13 @@ class SegmentMemoryArchive:
         return torch.where(indices >= 0, (indices + self.head) % self.capacity, indices)
 
 
+def _check_errors_if_asked() -> None:
+    """With ``GRMX_CHECK_ERRORS`` set, raise if a kernel of the pass reported a failure through the device
+    error word (``cuda_ops.check_device_errors``); never during stream capture, where nothing may wait."""
+    if cuda_ops._checking_each_call() and not torch.cuda.is_current_stream_capturing():
+        cuda_ops.check_device_errors()
+
+
 def _linear(x: Tensor, params: Dict[str, Tensor], name: str) -> Tensor:
     return F.linear(x, params[f"{name}.weight"], params.get(f"{name}.bias"))
 
@@ -367,12 +374,15 @@ class SegmentMemoryRunner:
         B, T, _ = x_seq.shape
         L = self.segment_length
         if self.whole_sequence_applies(x_seq, reset_memory):
-            return self._run_whole_sequence(x_seq, c_init, reset_memory, return_routes)
-        if T > 0 and T % L == 0:
+            result = self._run_whole_sequence(x_seq, c_init, reset_memory, return_routes)
+        elif T > 0 and T % L == 0:
             x_sm = x_seq.reshape(B, T // L, L, -1).transpose(0, 1).contiguous()
             out, last_hidden, memory, aux = self._run(x_sm, True, c_init, reset_memory, return_routes)
-            return out.transpose(0, 1).reshape(B, T, -1), last_hidden, memory, aux
-        return self._run(x_seq, False, c_init, reset_memory, return_routes)
+            result = out.transpose(0, 1).reshape(B, T, -1), last_hidden, memory, aux
+        else:
+            result = self._run(x_seq, False, c_init, reset_memory, return_routes)
+        _check_errors_if_asked()
+        return result
 
     @torch.no_grad()
     def forward_segment_major(self, x_sm: Tensor, c_init: Optional[Tensor] = None, reset_memory: bool = False,
@@ -672,6 +682,7 @@ class StackedSegmentMemoryRunner:
         y = F.linear(h, p[f"{pre}output_proj.weight"], p.get(f"{pre}output_proj.bias"))
         if self.language_model:
             y = F.linear(y, p["output_layer.weight"], p.get("output_layer.bias"))
+        _check_errors_if_asked()
         return y, torch.stack(finals, dim=0)
 
 

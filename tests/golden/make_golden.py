@@ -27,6 +27,7 @@ reference's Python implementation on CPU in float32:
 from __future__ import annotations
 
 import argparse
+import os
 import sys
 from pathlib import Path
 
@@ -236,7 +237,9 @@ def model_cfg4_case():
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("--reference", type=Path, default=Path("/root/reference"))
+    parser.add_argument("--reference", type=Path,
+                        default=Path(os.environ.get("GRM_REFERENCE_ROOT", "") or HERE.parents[2] / "reference"),
+                        help="reference checkout (default: $GRM_REFERENCE_ROOT, else a `reference` folder beside the repository)")
     parser.add_argument("--only", default="", help="generate only this fixture (e.g. model_cfg4)")
     args = parser.parse_args(argv)
     sys.dont_write_bytecode = True

@@ -62,6 +62,30 @@ def test_argument_errors_need_no_gpu(lib):
     assert lib.grmx_chunk_scan_bwd(*([None] * 10), 1, 4, 8, 8, 0.97, 0, 0, 0, None) == 1
 
 
+def test_static_workspace_admission_is_decided_on_the_host(lib):
+    # The allocation-free scan refuses a call whose cut needs more than the built-in array holds.  On a
+    # B200 (148 multiprocessors) no shape gets there, so the decision is tested as the host computation
+    # it is: the workspace a shape needs on a device of a given size, and the admission test on it.
+    cap = lib.grmx_static_scratch_capacity()
+    assert cap == 4 << 20
+    state = 64 * 64 * 4
+    on_b200 = lib.grmx_chunk_scan_scratch_bytes_on(64, 2048, 64, 64, 148)
+    assert 0 < on_b200 <= cap and on_b200 % state == 0
+    assert lib.grmx_static_scratch_admits(on_b200) == 0
+    assert lib.grmx_static_scratch_admits(cap) == 0
+    # a (fictitious) device of 4096 multiprocessors would cut 64 rows x 128 chunks far finer
+    on_giant = lib.grmx_chunk_scan_scratch_bytes_on(64, 16384, 64, 64, 4096)
+    assert on_giant > cap
+    assert lib.grmx_static_scratch_admits(on_giant) == 2
+    text = lib.grmx_last_error()
+    assert b"built-in one holds 4194304" in text and str(on_giant).encode() in text
+    assert lib.grmx_static_scratch_admits(cap + 1) == 2
+    assert lib.grmx_static_scratch_admits(-1) == 1
+    # wide heads are never cut over the workspace; a shape outside the tensor-core scan needs none
+    assert lib.grmx_chunk_scan_scratch_bytes_on(8, 4096, 128, 128, 148) == 0
+    assert lib.grmx_chunk_scan_scratch_bytes_on(0, 4096, 64, 64, 148) == 0
+
+
 def test_cuda_ops_public_surface_matches_the_reference():
     assert cuda_ops.__all__ == [
         "cuda_apply_query", "cuda_batched_memory_gather", "cuda_chunk_update", "get_grm_cuda_runtime_status",
