@@ -326,6 +326,75 @@ def retrieve_fuse(archive, indices, gates, queries, online=None, ln_weight=None,
     return fused
 
 
+# --------------------------------------------------------------------------- #
+# the single-layer model: segment loop over the pieces above
+# --------------------------------------------------------------------------- #
+
+def segment_model_forward(params: Dict[str, np.ndarray], x, *, segment_length: int, retrieval_top_k: int,
+                          memory_capacity_segments: int, memory_decay: float = 0.97, mode: str = "residual",
+                          eps: float = 1e-5):
+    """``SegmentRecurrentMemoryModel.forward`` (grm/core/paper_grm.py:647-747) in float64, dropout off,
+    ``memory_initialization_mode='checkpoint'``, zero start state, empty archive.
+
+    Per segment: project and L2-normalise (``:491-493``, ``F.normalize`` eps 1e-6), scan (``:495``), route every
+    token over the summaries of the archived segments (``:566-589``: bias-free projections, scale
+    ``1/sqrt(route_dim)``, top-k or identity order, softmax over the selected scores), apply the token's
+    query to the selected memories (``:301-307``), fuse (``:604-611``), project (``:709``), then archive the
+    segment-end memory with the mean of the segment's inputs (``:522-523,721-725``), oldest evicted first.
+    Returns ``(outputs [B,T,out], hidden_states [B,T,H], memory_final [B,H,K], routes)`` with
+    ``routes[i] = (indices, gates)`` of the i-th segment that saw a non-empty archive.
+    """
+    p = {k: np.asarray(v, dtype=np.float64) for k, v in params.items()}
+    x = np.asarray(x, dtype=np.float64)
+    B, T, _ = x.shape
+
+    def linear(name, t):
+        y = t @ p[f"{name}.weight"].T
+        return y + p[f"{name}.bias"] if f"{name}.bias" in p else y
+
+    def unit(t):
+        return t / np.maximum(np.linalg.norm(t, axis=-1, keepdims=True), 1e-6)
+
+    H, K = p["memory_cell.value_proj.weight"].shape[0], p["memory_cell.key_proj.weight"].shape[0]
+    route_dim = p["gating_unit.query_projection.weight"].shape[0]
+    fusion_params = {k[len("aggregator."):]: v for k, v in p.items() if k.startswith("aggregator.")}
+    memory = np.zeros((B, H, K))
+    archive, summaries = [], []
+    hidden_all, routes = [], []
+    for s0 in range(0, T, segment_length):
+        seg = x[:, s0:s0 + segment_length]
+        k, v, q = unit(linear("memory_cell.key_proj", seg)), linear("memory_cell.value_proj", seg), \
+            unit(linear("memory_cell.query_proj", seg))
+        h_online, memory = chunk_update_sequential(k, v, q, memory, memory_decay)
+        if archive:
+            keys = np.stack(summaries, axis=1)
+            scores = (seg @ p["gating_unit.query_projection.weight"].T) @ \
+                np.swapaxes(keys @ p["gating_unit.key_projection.weight"].T, 1, 2) / math.sqrt(route_dim)
+            idx, gates = topk_route(scores.astype(np.float32), retrieval_top_k)
+            R = min(retrieval_top_k, len(archive))
+            idx, gates = idx[..., :R], gates[..., :R]
+            # gates from the float64 scores, so that this restatement stays a float64 one
+            sel = np.take_along_axis(scores, idx, axis=-1)
+            e = np.exp(sel - sel.max(axis=-1, keepdims=True))
+            gates64 = e / e.sum(axis=-1, keepdims=True)
+            stack = np.stack(archive, axis=1)                                   # [B, S, H, K]
+            retrieved = np.einsum("bcrhk,bck->bcrh", stack[np.arange(B)[:, None, None], idx], q)
+            C = seg.shape[1]
+            fused = retrieved_state_fusion(h_online.reshape(B * C, H), retrieved.reshape(B * C, R, H),
+                                           gates64.reshape(B * C, R), mode, fusion_params, eps).reshape(B, C, H)
+            routes.append((idx, gates))
+        else:
+            fused = h_online                                                      # paper_grm.py:620-621
+        hidden_all.append(fused)
+        archive.append(memory.copy())
+        summaries.append(seg.mean(axis=1))
+        if len(archive) > memory_capacity_segments:
+            archive.pop(0)
+            summaries.pop(0)
+    hidden = np.concatenate(hidden_all, axis=1) if hidden_all else np.zeros((B, 0, H))
+    return linear("output_proj", hidden), hidden, memory, routes
+
+
 def rel_err(actual, expected) -> float:
     """``max|a-b| / max|b|`` -- the parity metric the tolerances are stated in."""
     a = np.asarray(actual, dtype=np.float64)

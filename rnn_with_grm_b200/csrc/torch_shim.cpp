@@ -274,6 +274,30 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> topk_route_cuda(const at::Tensor&
   return {gates, idx, scores};
 }
 
+// selection and gates on scores the caller holds (after masking with -inf, say): [B,Q,S] -> gates, indices [B,Q,top_k]
+std::tuple<at::Tensor, at::Tensor> topk_select_cuda(const at::Tensor& scores, const c10::optional<at::Tensor>& visible,
+                                                    int64_t top_k, double temperature) {
+  TORCH_CHECK(scores.dim() == 3, "scores must have shape [B, Q, S]");
+  require_cuda(scores, "scores");
+  c10::cuda::CUDAGuard guard(scores.device());
+  auto sc = scores.to(at::kFloat).contiguous();
+  const int64_t B = sc.size(0), Q = sc.size(1), S = sc.size(2);
+  at::Tensor vis;
+  const int32_t* vis_ptr = nullptr;
+  if (visible.has_value() && visible->defined()) {
+    require_cuda(*visible, "visible");
+    TORCH_CHECK(visible->numel() == Q, "visible must hold one count per query");
+    vis = visible->to(at::kInt).contiguous();
+    vis_ptr = vis.data_ptr<int32_t>();
+  }
+  auto idx = at::empty({B, Q, top_k}, sc.options().dtype(at::kLong));
+  auto gates = at::empty({B, Q, top_k}, sc.options());
+  check_status(grmx_topk_select(sc.data_ptr<float>(), vis_ptr, B, Q, S, static_cast<int>(top_k),
+                                static_cast<float>(temperature), idx.data_ptr<int64_t>(), gates.data_ptr<float>(),
+                                current_stream()));
+  return {gates, idx};
+}
+
 // states [B,Q,S,H] (fp32 or bf16), indices [B,Q,R], gates [B,Q,R] -> [B,Q,H] in the dtype of states
 at::Tensor select_fuse_cuda(const at::Tensor& states, const at::Tensor& indices, const at::Tensor& gates,
                             const c10::optional<at::Tensor>& online, const c10::optional<at::Tensor>& ln_weight,
@@ -440,6 +464,7 @@ TORCH_LIBRARY_IMPL(grm_cuda, CUDA, m) {
 TORCH_LIBRARY(grmx, m) {
   m.def("linear_scan(Tensor keys, Tensor values, Tensor queries, Tensor memory, float decay, float update_coeff, float hidden_scale, float memory_out_scale, bool reverse, bool first_step_no_decay, int path) -> (Tensor hidden, Tensor memory_out)");
   m.def("topk_route(Tensor queries, Tensor keys, Tensor? visible, int top_k, float scale, float temperature, bool return_scores) -> (Tensor gates, Tensor indices, Tensor scores)");
+  m.def("topk_select(Tensor scores, Tensor? visible, int top_k, float temperature) -> (Tensor gates, Tensor indices)");
   m.def("retrieve_fuse(Tensor archive, Tensor indices, Tensor? gates, Tensor queries, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
   m.def("chunk_scan_segments(Tensor keys, Tensor values, Tensor queries, Tensor memory, float decay, Tensor(a!) archive, int first_slot, int segment_tokens) -> (Tensor hidden, Tensor memory_out)");
   m.def("l2_normalize(Tensor x, float eps, bool to_bfloat16) -> Tensor");
@@ -450,6 +475,7 @@ TORCH_LIBRARY(grmx, m) {
 TORCH_LIBRARY_IMPL(grmx, CUDA, m) {
   m.impl("linear_scan", linear_scan_cuda);
   m.impl("topk_route", topk_route_cuda);
+  m.impl("topk_select", topk_select_cuda);
   m.impl("retrieve_fuse", retrieve_fuse_cuda);
   m.impl("select_fuse", select_fuse_cuda);
   m.impl("archive_push", archive_push_cuda);

@@ -625,6 +625,9 @@ class StackedSegmentMemoryRunner:
             sub = {k[len(base):]: v for k, v in params.items() if k.startswith(base)}
             self.layers.append(SegmentMemoryRunner(sub, **layer_kwargs))
         self.num_layers = num_layers
+        # False: stop after the stack's own output projection (the 512 -> vocabulary layer of the language-model
+        # wrapper is not part of the memory path; timing with and without it separates the two)
+        self.vocabulary_projection = True
         self._unit_routes: Dict[Tuple[int, str], Tuple[Tensor, Tensor]] = {}
         self._fp32_cache: Dict[int, Tuple[Tensor, Tensor, int]] = {}
 
@@ -680,7 +683,7 @@ class StackedSegmentMemoryRunner:
         if segment_major:
             h = h.transpose(0, 1).reshape(B, T, h.shape[-1])
         y = F.linear(h, p[f"{pre}output_proj.weight"], p.get(f"{pre}output_proj.bias"))
-        if self.language_model:
+        if self.language_model and self.vocabulary_projection:
             y = F.linear(y, p["output_layer.weight"], p.get("output_layer.bias"))
         _check_errors_if_asked()
         return y, torch.stack(finals, dim=0)

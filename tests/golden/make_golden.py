@@ -19,6 +19,12 @@ reference's Python implementation on CPU in float32:
 * ``model_cfg4.npz``      -- samples of the 4-layer ``SegmentMemoryLanguageModel`` forward at config 4
                              (B=8, T=8192, hidden 512, vocab 32768; ``--only model_cfg4``, ~2 min),
                              weights rebuilt from ``seeded_weights.py``.
+* ``fusion_cfg3_*.npz``   -- ``RetrievedStateFusion(64, mode)`` as the retrieval configuration builds it
+                             (``torch.manual_seed(0)``, default initialisation): weights, a few input rows
+                             and the module's outputs on them.
+* ``model_fusion_*.npz``  -- the same model class, smaller (hidden 64, key dim 32, segment 64, four
+                             segments), with ``retrieval_fusion_mode`` concat / gate / linear:
+                             weights, inputs, outputs and final state.
 * ``model_cfg1.npz``      -- ``SegmentRecurrentMemoryModel`` forward on the single-layer
                              adding-problem configuration (weights, inputs, outputs, final
                              state and every segment's routing indices and gates).
@@ -151,6 +157,24 @@ def fusion_cases():
                             gates=gates.numpy(), fused=fused.numpy(), eps=np.float64(mod.layer_norm.eps), **params)
 
 
+def fusion_cfg3_cases():
+    """The fusion module at the hidden size of the top-k retrieval configuration (d_v = 64, four routes)."""
+    from grm.core.aggregator import RetrievedStateFusion
+
+    for mode in ("residual", "concat", "gate", "linear"):
+        torch.manual_seed(0)
+        mod = RetrievedStateFusion(hidden_size=64, retrieval_fusion_mode=mode, dropout=0.0).eval()
+        g = torch.Generator().manual_seed(33)
+        online = torch.randn(12, 64, generator=g)
+        retrieved = torch.randn(12, 4, 64, generator=g)
+        gates = torch.softmax(torch.randn(12, 4, generator=g), dim=-1)
+        with torch.no_grad():
+            fused = mod(h_online=online, cached_states=retrieved, gates=gates)
+        params = {f"param::{k}": v.detach().numpy() for k, v in mod.state_dict().items()}
+        np.savez_compressed(HERE / f"fusion_cfg3_{mode}.npz", online=online.numpy(), retrieved=retrieved.numpy(),
+                            gates=gates.numpy(), fused=fused.numpy(), eps=np.float64(mod.layer_norm.eps), **params)
+
+
 def adding_problem_inputs(batch, seq_len, seed):
     """Channel 0 ~ U[0,1); channel 1 marks two positions, one in each half."""
     g = torch.Generator().manual_seed(seed)
@@ -195,6 +219,33 @@ def model_cfg1_case():
         memory_final=memory_final.numpy(), hidden_states=aux["hidden_states"].numpy(),
         num_segments=np.int64(aux["num_segments"]), **payload,
     )
+
+
+def model_fusion_cases():
+    """The single-layer model with each weight-bearing fusion rule, small enough to keep the weights in
+    the fixture."""
+    from grm.core.paper_grm import SegmentRecurrentMemoryModel
+
+    for seed, mode in enumerate(("concat", "gate", "linear"), start=40):
+        torch.manual_seed(seed)
+        model = SegmentRecurrentMemoryModel(
+            input_size=2, hidden_size=64, output_size=1, segment_length=64, memory_key_dim=32,
+            retrieval_top_k=2, memory_capacity_segments=8, memory_storage_dtype=torch.float32,
+            recomputation_ratio=0.0, dropout=0.0, retrieval_fusion_mode=mode, cuda_cpp_debug_fallback=True,
+        ).eval()
+        with torch.no_grad():      # LayerNorm affine away from (1, 0), so that a missing affine shows
+            model.aggregator.layer_norm.weight.uniform_(0.5, 1.5)
+            model.aggregator.layer_norm.bias.uniform_(-0.5, 0.5)
+        x = adding_problem_inputs(2, 256, seed=seed)
+        with torch.no_grad():
+            outputs, h_final, memory_final, aux = model(x, reset_memory=True, return_hidden_states=True)
+        payload = {f"param::{k}": v.detach().numpy() for k, v in model.state_dict().items()
+                   if isinstance(v, torch.Tensor) and not k.startswith("memory_bank")}
+        np.savez_compressed(
+            HERE / f"model_fusion_{mode}.npz", x=x.numpy(), outputs=outputs.numpy(), h_final=h_final.numpy(),
+            memory_final=memory_final.numpy(), hidden_states=aux["hidden_states"].numpy(),
+            num_segments=np.int64(aux["num_segments"]), **payload,
+        )
 
 
 def model_cfg4_case():
@@ -248,6 +299,12 @@ def main(argv=None) -> int:
     if args.only == "model_cfg4":
         model_cfg4_case()
         return 0
+    if args.only == "model_fusion":
+        model_fusion_cases()
+        return 0
+    if args.only == "fusion_cfg3":
+        fusion_cfg3_cases()
+        return 0
     chunk_case("small", 1, B=2, T=8, K=8, H=16, decay=0.97)        # shape of examples/test_grm.py:29-37
     chunk_case("ragged", 2, B=3, T=67, K=6, H=5, decay=0.9)
     chunk_case("cfg1", 3, B=2, T=128, K=64, H=128, decay=0.97, zero_state=True)
@@ -256,7 +313,9 @@ def main(argv=None) -> int:
     gather_case()
     retriever_cases()
     fusion_cases()
+    fusion_cfg3_cases()
     model_cfg1_case()
+    model_fusion_cases()
     total = sum(p.stat().st_size for p in HERE.glob("*.npz"))
     print(f"wrote {len(list(HERE.glob('*.npz')))} fixtures, {total / 1024:.0f} KiB")
     return 0

@@ -136,29 +136,6 @@ def test_eviction_does_not_change_results_when_capacity_suffices(golden):
     assert torch.equal(out_small[:, :384], out_big[:, :384]) and not torch.equal(out_small[:, 384:], out_big[:, 384:])
 
 
-@pytest.mark.parametrize("mode", ["concat", "gate", "linear"])
-def test_other_fusion_rules_run_through_the_contrib_kernel(golden, mode):
-    g = golden("model_cfg1")
-    f = golden(f"fusion_{mode}")
-    runner = _runner(g, retrieval_fusion_mode=mode)
-    hidden = runner.hidden
-    torch.manual_seed(0)
-    for key, value in f.items():          # same parameter names as the fixture, sized for this model
-        if not key.startswith("param::") or "layer_norm" in key:
-            continue
-        name = "aggregator." + key[len("param::"):]
-        if value.ndim == 1:
-            runner.p[name] = torch.zeros(hidden, device=DEV)
-        else:
-            cols = 2 * hidden if value.shape[1] == 2 * value.shape[0] else hidden
-            runner.p[name] = torch.randn(hidden, cols, device=DEV) * 0.05
-    x = torch.from_numpy(g["x"]).to(DEV)
-    out, _, memory, _ = runner.forward(x, reset_memory=True)
-    assert torch.isfinite(out).all()
-    assert go.rel_err(memory.cpu().numpy(), g["memory_final"]) < FP32_TOL      # the scan does not depend on the rule
-    assert go.rel_err(out[:, :128].cpu().numpy(), g["outputs"][:, :128]) < FP32_TOL   # first segment: no fusion at all
-
-
 def _cfg4_runner(g, dtype):
     import ast
     import sys

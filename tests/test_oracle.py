@@ -152,12 +152,41 @@ def test_c_scores_agree_with_double_precision():
     assert go.rel_err(oracle.c_route_scores(q, k, 0.125), go.route_scores(q, k, 0.125)) < FP32_TOL
 
 
+@pytest.mark.parametrize("size", ["", "cfg3_"])
 @pytest.mark.parametrize("mode", ["residual", "concat", "gate", "linear"])
-def test_fusion_matches_reference(golden, mode):
-    g = golden(f"fusion_{mode}")
+def test_fusion_matches_reference(golden, mode, size):
+    g = golden(f"fusion_{size}{mode}")
     params = {k[len("param::"):]: v for k, v in g.items() if k.startswith("param::")}
     fused = go.retrieved_state_fusion(g["online"], g["retrieved"], g["gates"], mode, params, float(g["eps"]))
     assert go.rel_err(fused, g["fused"]) < FP32_TOL
+
+
+def test_model_restatement_matches_reference_model_cfg1(golden):
+    """Config 1: the reference's single-layer model forward, fp32 -- outputs, every token's fused state,
+    the final memory and every segment's routing decisions."""
+    g = golden("model_cfg1")
+    params = {k[len("param::"):]: v for k, v in g.items() if k.startswith("param::")}
+    out, hidden, memory, routes = go.segment_model_forward(params, g["x"], segment_length=128, retrieval_top_k=2,
+                                                           memory_capacity_segments=8)
+    assert go.rel_err(out, g["outputs"]) < FP32_TOL
+    assert go.rel_err(hidden, g["hidden_states"]) < FP32_TOL
+    assert go.rel_err(memory, g["memory_final"]) < FP32_TOL
+    assert len(routes) == 3
+    for i, (idx, gates) in enumerate(routes, start=1):
+        assert np.array_equal(idx, g[f"route{i}_indices"])
+        assert go.rel_err(gates, g[f"route{i}_gates"]) < FP32_TOL
+
+
+@pytest.mark.parametrize("mode", ["concat", "gate", "linear"])
+def test_model_restatement_matches_reference_model_with_other_fusion_rules(golden, mode):
+    g = golden(f"model_fusion_{mode}")
+    params = {k[len("param::"):]: v for k, v in g.items() if k.startswith("param::")}
+    out, hidden, memory, routes = go.segment_model_forward(params, g["x"], segment_length=64, retrieval_top_k=2,
+                                                           memory_capacity_segments=8, mode=mode)
+    assert int(g["num_segments"]) == 4 and len(routes) == 3
+    assert go.rel_err(hidden, g["hidden_states"]) < FP32_TOL
+    assert go.rel_err(out, g["outputs"]) < FP32_TOL
+    assert go.rel_err(memory, g["memory_final"]) < FP32_TOL
 
 
 def test_retrieve_fuse_chain_equals_its_parts(golden):
