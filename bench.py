@@ -458,7 +458,7 @@ def run_scale_out(args, rank, world, device, hbm_peak):
     runner = so.SlabRunner(shape, slab_rows, device)
     stream = torch.cuda.current_stream().cuda_stream
     flat = torch.zeros(max(len(samples), 1), so.sample_vector_len(shape), device=device)
-    slab_ms, launches = [], 0
+    slab_ms, scan_ms, launches = [], [], 0
     if world > 1:
         torch.distributed.barrier()
     torch.cuda.synchronize()
@@ -473,12 +473,13 @@ def run_scale_out(args, rank, world, device, hbm_peak):
         n = runner.generate(r0, r1, 0, host_rows)       # input generation: outside the timed region
         runner.segment_means(n)
         torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0, e1, em = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         e0.record()
-        launches += runner.launch(n, stream)
+        launches += runner.launch(n, stream, after_scan=em.record)
         e1.record()
         torch.cuda.synchronize()
         slab_ms.append(e0.elapsed_time(e1))
+        scan_ms.append(e0.elapsed_time(em))
         for j, row in enumerate(samples):
             if r0 <= row < r1:
                 i = row - r0
@@ -514,6 +515,8 @@ def run_scale_out(args, rank, world, device, hbm_peak):
         "slabs_per_gpu": len(slabs),
         "device_bytes_per_slab": runner.bytes_held(),
         "ms": total_ms,
+        "scan_ms_rank0": sum(scan_ms),
+        "retrieval_ms_rank0": sum(slab_ms) - sum(scan_ms),
         "tokens_per_s": shape.batch_tokens / (total_ms * 1e-3),
         "row_token_units_per_s": shape.rows * shape.tokens / (total_ms * 1e-3),
         "gpu_launches": launches,
@@ -986,7 +989,8 @@ def main(argv=None) -> int:
                         help="no CPU baseline and no other workloads (small footprint for profiling)")
     parser.add_argument("--skip-scale-out", action="store_true", help="do not run the sharded configuration 5")
     parser.add_argument("--scale-out-rows", type=int, default=4096, help="rows of configuration 5 (all GPUs together)")
-    parser.add_argument("--slab-rows", type=int, default=256, help="rows a GPU holds at a time in configuration 5")
+    parser.add_argument("--slab-rows", type=int, default=296,
+                        help="rows a GPU holds at a time in configuration 5 (296 rows x 2 value blocks = 4 CTAs per SM of a B200)")
     parser.add_argument("--verify-rows", type=int, default=2, help="rows per rank checked against the oracle")
     parser.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     parser.add_argument("--with-workspace", action="store_true",

@@ -37,6 +37,7 @@ CUDA_SOURCES = [
     "tc_host.cu",
     "chunk_scan_tc_pipe.cu",
     "chunk_scan_tc_split.cu",
+    "chunk_scan_tc_wide.cu",
     "apply_query.cu",
     "gather.cu",
     "topk_route.cu",

@@ -167,7 +167,7 @@ int grmx_chunk_scan_fwd_segments(const void* keys, const void* values, const voi
   if (!grmx::scan_tcgen05_supported(p, io_dtype, state_dtype, &why) || !grmx::scan_tcgen05_pipe_supported(p)) {
     return grmx::fail(GRMX_ERR_UNSUPPORTED, "%s: needs the tensor-core scan: %s", who, why);
   }
-  return grmx::launch_scan_tcgen05_selfcut(p, static_cast<cudaStream_t>(stream));
+  return grmx::launch_scan_tcgen05(p, static_cast<cudaStream_t>(stream));
 }
 
 int64_t grmx_chunk_scan_scratch_bytes(int64_t B, int64_t T, int64_t K, int64_t H, int io_dtype,

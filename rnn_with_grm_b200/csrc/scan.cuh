@@ -56,6 +56,11 @@ struct SplitInfo {
 bool scan_tcgen05_pipe_supported(const ScanParams& p);
 int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaStream_t stream);
 
+// The same for heads of d_k = 128: one CTA per (row, 64 value features) with both key halves in one
+// product, every q / k / v tile read once and every output tile written once.  Forward scans only.
+bool scan_tcgen05_wide_supported(const ScanParams& p);
+int launch_scan_tcgen05_wide(const ScanParams& p, cudaStream_t stream);
+
 // Cutting along T: bytes of scratch the cut needs for this call (0 when a cut would not help or
 // the shape is not covered), and the launch that runs the piece-state kernel followed by the scan.
 int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p, int sm_count = 0);   // 0: the current device

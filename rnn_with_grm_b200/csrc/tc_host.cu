@@ -169,6 +169,9 @@ bool scan_tcgen05_supported(const ScanParams& p, int io_dtype, int state_dtype, 
   return true;
 }
 
-int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream) { return launch_scan_tcgen05_selfcut(p, stream); }
+int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream) {
+  if (scan_tcgen05_wide_supported(p)) return launch_scan_tcgen05_wide(p, stream);
+  return launch_scan_tcgen05_selfcut(p, stream);
+}
 
 }  // namespace grmx

@@ -39,6 +39,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
   return ok;
 }
 
+// Non-blocking test of a barrier phase (try_wait may suspend the thread for a while; this never does).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the
 // barrier did not flip within the limit or another thread already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
@@ -196,6 +211,18 @@ __device__ __forceinline__ void tma_load_3d_if(uint32_t leader, void* dst, const
       "[%0], [%1, {%3, %4, %5}], [%2];\n\t"
       "}" ::"r"(smem_u32(dst)),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(leader)
+      : "memory");
+}
+
+// Ask a tile into L2 (no shared memory, no barrier): the later load of the same box finds it there.
+__device__ __forceinline__ void tma_prefetch_3d_if(uint32_t leader, const CUtensorMap* map, int x, int y, int z) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %4, 0;\n\t"
+      "@q cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n\t"
+      "}" ::"l"(reinterpret_cast<uint64_t>(map)),
+      "r"(x), "r"(y), "r"(z), "r"(leader)
       : "memory");
 }
 

@@ -153,15 +153,18 @@ class SlabRunner:
         torch.mean(self.q[:n].view(n, S, L, d), dim=2, dtype=torch.float32, out=self.seg_q[:n])
         torch.mean(self.k[:n].view(n, S, L, d), dim=2, dtype=torch.float32, out=self.seg_k[:n])
 
-    def launch(self, n: int, stream: int) -> int:
+    def launch(self, n: int, stream: int, after_scan=None) -> int:
         """Scan with segment snapshots -> routing -> fused retrieval for the first ``n`` rows; returns the
-        number of kernel launches enqueued."""
+        number of kernel launches enqueued.  ``after_scan`` is called between the scan and the retrieval
+        (the benchmark records an event there)."""
         sh, lib, cabi = self.shape, self.lib, self.cabi
         before = lib.grmx_launch_count()
         cabi.check(lib.grmx_chunk_scan_fwd_segments(
             self.k.data_ptr(), self.v.data_ptr(), self.q.data_ptr(), self.m_in.data_ptr(), self.hidden.data_ptr(),
             self.m_out.data_ptr(), self.archive.data_ptr(), sh.segments, 0, sh.segment, n, sh.tokens, sh.dim, sh.dim,
             sh.decay, cabi.BF16, cabi.F32, stream))
+        if after_scan is not None:
+            after_scan()
         cabi.check(lib.grmx_topk_route(self.seg_q.data_ptr(), self.seg_k.data_ptr(), self.visible.data_ptr(), n,
                                        sh.segments, sh.segments, sh.dim, sh.top_k, 1.0, 1.0, self.indices.data_ptr(),
                                        self.gates.data_ptr(), None, stream))

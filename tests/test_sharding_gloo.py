@@ -41,6 +41,8 @@ def test_scale_out_plan_covers_every_row_once_and_samples_sit_inside():
         for rank in range(world):
             slabs = so.plan_slabs(shape, rank, world, 256)
             assert len(slabs) == 16 // world and all(b - a == 256 for a, b in slabs)
+            ragged = so.plan_slabs(shape, rank, world, 296)          # the last slab of a rank takes what is left
+            assert sum(b - a for a, b in ragged) == 4096 // world and all(b - a == 296 for a, b in ragged[:-1])
             covered += [r for a, b in slabs for r in (a, b)]
             start, stop = row_range(shape.rows, rank, world)
             picks = so.sample_rows(shape, rank, world, 2)
