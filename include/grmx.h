@@ -310,6 +310,26 @@ int grmx_retrieve_fuse(const float* archive, const int64_t* indices, const float
                        int64_t Q, int64_t R, int64_t H, int64_t K, int mode, void* stream);
 
 /*
+ * grmx_retrieve_fuse for per-token routing on the tensor cores: every token of a batch row chooses R of
+ * the row's S archived matrices, all in bf16 (archive_bf16 [B,S,H,K], queries_bf16 [B,Q,K], online_bf16 and
+ * out_bf16 [B,Q,H]; indices int64 and gates float32 [B,Q,R] as in grmx_retrieve_fuse).  For a tile of 128
+ * tokens the kernel accumulates one product per chosen slot, (gate-scaled queries) x (the slot's matrix),
+ * in a TMEM accumulator, so neither the gathered matrices nor per-candidate states ever exist in memory;
+ * then residual + LayerNorm (GRMX_FUSE_RESIDUAL_LN; a token without a live route keeps its online state)
+ * or the plain gate-weighted contribution (GRMX_FUSE_CONTRIB).  Sums in fp32; the gates enter the product
+ * rounded to bf16.  Covers K == 64, H a multiple of 64 up to 512, 1 <= S <= 32, 1 <= R <= 8, 16-byte
+ * aligned tensors; GRMX_ERR_UNSUPPORTED otherwise (use grmx_retrieve_fuse).
+ *
+ * Replaces the same chain as grmx_retrieve_fuse where the reference runs it per token
+ * (grm/core/paper_grm.py:613-645: rank-5 gather, rank-5 apply-query grm/csrc/apply_query.cu:14-75,
+ * RetrievedStateFusion on B*C rows).
+ */
+int grmx_retrieve_fuse_tc(const void* archive_bf16, const int64_t* indices, const float* gates,
+                          const void* queries_bf16, const void* online_bf16, const float* ln_weight,
+                          const float* ln_bias, float ln_eps, void* out_bf16, int64_t B, int64_t S, int64_t Q,
+                          int64_t R, int64_t H, int64_t K, int mode, void* stream);
+
+/*
  * The selection half of grmx_retrieve_fuse for callers that have already applied the query to every
  * candidate: states [B,Q,S,H] (states[b,q,s,:] = M[b,s] q[b,q], e.g. one batched GEMM per batch row when
  * all Q tokens of a segment choose among the same S archived matrices), indices int64 [B,Q,R] into S

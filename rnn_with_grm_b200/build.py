@@ -42,6 +42,7 @@ CUDA_SOURCES = [
     "gather.cu",
     "topk_route.cu",
     "retrieve_fuse.cu",
+    "retrieve_fuse_tc.cu",
     "select_fuse.cu",
     "archive_push.cu",
     "normalize_rows.cu",

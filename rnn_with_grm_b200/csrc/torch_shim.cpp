@@ -443,6 +443,55 @@ at::Tensor retrieve_fuse_cuda(const at::Tensor& archive, const at::Tensor& indic
   return out;
 }
 
+// bf16 archive ring [B,S,H,K], bf16 queries [B,Q,K], bf16 online [B,Q,H] -> bf16 [B,Q,H] (tensor-core retrieval)
+at::Tensor retrieve_fuse_tc_cuda(const at::Tensor& archive, const at::Tensor& indices, const at::Tensor& gates,
+                                 const at::Tensor& queries, const c10::optional<at::Tensor>& online,
+                                 const c10::optional<at::Tensor>& ln_weight, const c10::optional<at::Tensor>& ln_bias,
+                                 double ln_eps, int64_t mode) {
+  TORCH_CHECK(archive.dim() == 4, "archive must have shape [B, S, H, K]");
+  TORCH_CHECK(indices.dim() == 3 && gates.dim() == 3 && indices.sizes() == gates.sizes(),
+              "indices and gates must have shape [B, Q, R]");
+  TORCH_CHECK(queries.dim() == 3, "queries must have shape [B, Q, K]");
+  TORCH_CHECK(archive.size(0) == indices.size(0) && archive.size(0) == queries.size(0), "batch dim mismatch");
+  TORCH_CHECK(indices.size(1) == queries.size(1), "query dim mismatch between indices and queries");
+  TORCH_CHECK(archive.size(3) == queries.size(2), "key dim mismatch between archive and queries");
+  require_cuda(archive, "archive");
+  require_cuda(indices, "indices");
+  require_cuda(gates, "gates");
+  require_cuda(queries, "queries");
+  TORCH_CHECK(archive.scalar_type() == at::kBFloat16 && queries.scalar_type() == at::kBFloat16,
+              "archive and queries must be bfloat16");
+  c10::cuda::CUDAGuard guard(archive.device());
+  auto arch = archive.contiguous();
+  auto idx = indices.toType(at::kLong).contiguous();
+  auto g = gates.to(at::kFloat).contiguous();
+  auto q = queries.contiguous();
+  const int64_t B = arch.size(0), S = arch.size(1), H = arch.size(2), K = arch.size(3);
+  const int64_t Q = idx.size(1), R = idx.size(2);
+  at::Tensor o_keep, w_keep, b_keep;
+  const void* o_ptr = nullptr;
+  if (online.has_value() && online->defined()) {
+    require_cuda(*online, "online");
+    o_keep = online->to(at::kBFloat16).contiguous();
+    TORCH_CHECK(o_keep.sizes() == at::IntArrayRef({B, Q, H}), "online has the wrong shape");
+    o_ptr = o_keep.data_ptr();
+  }
+  auto opt = [&](const c10::optional<at::Tensor>& t, const char* name, at::Tensor& keep) -> const float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    require_cuda(*t, name);
+    keep = t->to(at::kFloat).contiguous();
+    TORCH_CHECK(keep.numel() == H, name, " has the wrong shape");
+    return keep.data_ptr<float>();
+  };
+  const float* w_ptr = opt(ln_weight, "ln_weight", w_keep);
+  const float* b_ptr = opt(ln_bias, "ln_bias", b_keep);
+  at::Tensor out = at::empty({B, Q, H}, arch.options());
+  check_status(grmx_retrieve_fuse_tc(arch.data_ptr(), idx.data_ptr<int64_t>(), g.data_ptr<float>(), q.data_ptr(), o_ptr,
+                                     w_ptr, b_ptr, static_cast<float>(ln_eps), out.data_ptr(), B, S, Q, R, H, K,
+                                     static_cast<int>(mode), current_stream()));
+  return out;
+}
+
 }  // namespace
 
 TORCH_LIBRARY(grm_cuda, m) {
@@ -466,6 +515,7 @@ TORCH_LIBRARY(grmx, m) {
   m.def("topk_route(Tensor queries, Tensor keys, Tensor? visible, int top_k, float scale, float temperature, bool return_scores) -> (Tensor gates, Tensor indices, Tensor scores)");
   m.def("topk_select(Tensor scores, Tensor? visible, int top_k, float temperature) -> (Tensor gates, Tensor indices)");
   m.def("retrieve_fuse(Tensor archive, Tensor indices, Tensor? gates, Tensor queries, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
+  m.def("retrieve_fuse_tc(Tensor archive, Tensor indices, Tensor gates, Tensor queries, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
   m.def("chunk_scan_segments(Tensor keys, Tensor values, Tensor queries, Tensor memory, float decay, Tensor(a!) archive, int first_slot, int segment_tokens) -> (Tensor hidden, Tensor memory_out)");
   m.def("l2_normalize(Tensor x, float eps, bool to_bfloat16) -> Tensor");
   m.def("archive_push(Tensor memory, Tensor(a!) archive, Tensor(b!)? shadow, int slot) -> ()");
@@ -477,6 +527,7 @@ TORCH_LIBRARY_IMPL(grmx, CUDA, m) {
   m.impl("topk_route", topk_route_cuda);
   m.impl("topk_select", topk_select_cuda);
   m.impl("retrieve_fuse", retrieve_fuse_cuda);
+  m.impl("retrieve_fuse_tc", retrieve_fuse_tc_cuda);
   m.impl("select_fuse", select_fuse_cuda);
   m.impl("archive_push", archive_push_cuda);
   m.impl("l2_normalize", l2_normalize_cuda);

@@ -234,6 +234,11 @@ class SegmentMemoryRunner:
         # launch plus one routing / selection pass for all tokens (see _run_whole_sequence).
         self.fuse_segments = True
         self.max_state_bytes = 1 << 30      # candidate states held at a time by the whole-sequence form
+        # bf16 activations with a 64-wide key: the retrieval runs on the tensor cores straight from the bf16
+        # ring (``torch.ops.grmx.retrieve_fuse_tc``), one accumulated product per chosen slot and token tile,
+        # and neither gathered matrices nor candidate states exist.  False: the batched GEMM over all
+        # candidates followed by ``select_fuse``.
+        self.tensor_core_retrieval = True
         self._route_query_weight: Optional[Tensor] = None
         self._fp32_cache: Dict[str, Tuple[Tensor, Tensor, int]] = {}
         self._visible_cache: Dict[Tuple[int, int, str], Tensor] = {}
@@ -318,6 +323,12 @@ class SegmentMemoryRunner:
         mem = mem.reshape(B, archive.count * self.hidden, self.key_dim).to(q_t.dtype)
         return torch.matmul(q_t, mem.transpose(1, 2)).view(B, C, archive.count, self.hidden)
 
+    def _tc_retrieval_applies(self, q: Tensor, routes: int) -> bool:
+        archive = self.archive
+        return (self.tensor_core_retrieval and q.is_cuda and q.dtype == torch.bfloat16 and archive is not None
+                and archive.memories_bf16 is not None and self.key_dim == 64 and self.hidden % 64 == 0
+                and self.hidden <= 512 and archive.capacity <= 32 and 1 <= routes <= 8)
+
     def _retrieve_and_fuse(self, q_n: Tensor, h_online: Tensor, gates: Tensor, indices: Tensor) -> Tensor:
         """``q_n``: the segment's normalised queries (paper_grm.py:301,312 recompute the same values)."""
         archive = self.archive
@@ -325,6 +336,14 @@ class SegmentMemoryRunner:
         ln_b = self._fp32_param("aggregator.layer_norm.bias") if self.use_layer_norm else None
         plain_residual = (self.mode == "residual" and self.use_layer_norm
                           and "aggregator.output_projection.weight" not in self.p)
+        if self._tc_retrieval_applies(q_n, indices.shape[2]):
+            phys = archive.physical_indices(indices)
+            if plain_residual:
+                return torch.ops.grmx.retrieve_fuse_tc(archive.memories_bf16, phys, gates, q_n, h_online, ln_w, ln_b,
+                                                       self.eps, FUSE_RESIDUAL_LN)
+            contrib = torch.ops.grmx.retrieve_fuse_tc(archive.memories_bf16, phys, gates, q_n, None, None, None,
+                                                      self.eps, FUSE_CONTRIB)
+            return self._fuse_rule(h_online, contrib)
         # queries x routes against candidates: the dense form reads every candidate once per batch row
         dense = self.dense_retrieval and indices.shape[1] * indices.shape[2] >= 4 * archive.count
         if dense:
@@ -459,13 +478,24 @@ class SegmentMemoryRunner:
             ln_b = self._fp32_param("aggregator.layer_norm.bias") if self.use_layer_norm else None
             plain_residual = (self.mode == "residual" and self.use_layer_norm
                               and "aggregator.output_projection.weight" not in self.p)
+            tensor_core = self._tc_retrieval_applies(q, indices.shape[2])
             # the candidate states of a block of segments at a time, at most ~1 GiB of them (one block at
             # config 4; four blocks, each with only the candidates its last segment sees, compute 40 %
             # less but measured slower: 5.24 against 4.92 ms)
             per_segment = B * L * held * self.hidden * 2
             block = max(1, min(n_seg, self.max_state_bytes // max(per_segment, 1)))
             pieces = []
-            for s0 in range(0, n_seg, block):
+            if tensor_core:
+                # all tokens at once, straight from the bf16 ring: a token's routes name slots below its own
+                # visible count only, so the later slots (already written by the scan) stay untouched
+                if plain_residual:
+                    pieces.append(torch.ops.grmx.retrieve_fuse_tc(archive.memories_bf16, indices, gates, q, hidden, ln_w,
+                                                                  ln_b, self.eps, FUSE_RESIDUAL_LN))
+                else:
+                    contrib = torch.ops.grmx.retrieve_fuse_tc(archive.memories_bf16, indices, gates, q, None, None, None,
+                                                              self.eps, FUSE_CONTRIB)
+                    pieces.append(self._fuse_rule(hidden, contrib))
+            for s0 in range(0, n_seg if not tensor_core else 0, block):
                 s1 = min(s0 + block, n_seg)
                 tok = slice(s0 * L, s1 * L)
                 slots = first + s1 - 1                                # the last segment of the block sees this many

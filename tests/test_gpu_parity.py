@@ -437,6 +437,64 @@ def test_select_fuse_equals_the_fused_chain_on_dense_candidates(dtype, tol, H):
 
 # --------------------------------------------------------------------------- chunk scan, tcgen05 path
 
+@pytest.mark.parametrize("B,S,Q,R,H,seg,mode", [(1, 3, 128, 2, 64, None, cabi.FUSE_RESIDUAL_LN),
+                                                (2, 5, 300, 2, 128, 64, cabi.FUSE_RESIDUAL_LN),
+                                                (2, 7, 257, 3, 192, 32, cabi.FUSE_CONTRIB),
+                                                (3, 15, 512, 4, 512, 32, cabi.FUSE_RESIDUAL_LN),
+                                                (1, 32, 384, 8, 256, None, cabi.FUSE_RESIDUAL_LN)])
+def test_tensor_core_retrieval_matches_the_fused_chain(B, S, Q, R, H, seg, mode):
+    """Per-token retrieval straight from the bf16 ring (one accumulated product per chosen slot and tile of
+    128 tokens) against gather -> apply-query -> gate-weighted sum -> residual LayerNorm in float64 on the
+    same bf16 values; causal visible counts leave early tokens with fewer routes or none (those keep their
+    online state untouched)."""
+    rng = np.random.default_rng(61 + Q)
+    arch = dev(rng.standard_normal((B, S, H, 64)).astype(np.float32), torch.bfloat16)
+    qv = rng.standard_normal((B, Q, 64)).astype(np.float32)
+    qv /= np.linalg.norm(qv, axis=-1, keepdims=True)
+    q = dev(qv, torch.bfloat16)
+    online = dev(rng.standard_normal((B, Q, H)).astype(np.float32), torch.bfloat16)
+    ln_w = dev(rng.uniform(0.5, 1.5, H).astype(np.float32))
+    ln_b = dev(rng.uniform(-0.5, 0.5, H).astype(np.float32))
+    visible = None if seg is None else np.minimum(np.arange(Q) // seg, S).astype(np.int32)
+    idx, gates = oracle.c_topk_select(rng.standard_normal((B, Q, S)).astype(np.float32), R, 1.0, visible)
+    got = gx.retrieve_fuse_tc(arch, dev(idx), dev(gates), q, online, ln_w, ln_b, 1e-5, mode)
+    assert got.dtype == torch.bfloat16 and cabi.device_error_word() == 0
+    if mode == cabi.FUSE_RESIDUAL_LN:
+        want = go.retrieve_fuse(host(arch), idx, gates, host(q), host(online), host(ln_w), host(ln_b), 1e-5)
+        if visible is not None:                                     # tokens that see no segment: passed through bit for bit
+            none = torch.from_numpy(visible == 0).to(DEV)
+            assert torch.equal(got[:, none], online[:, none])
+    else:
+        want = go.retrieve_fuse(host(arch), idx, gates, host(q), mode="contrib")
+    close(got, want, LOWP_TOL)
+    # the selection kernel on dense candidate states is the other route to the same result
+    states = torch.einsum("bshk,bqk->bqsh", arch.float(), q.float()).to(torch.bfloat16).contiguous()
+    other = gx.select_fuse(states, dev(idx), dev(gates), online, ln_w, ln_b, 1e-5, mode)
+    close(got, host(other), LOWP_TOL)
+
+
+def test_tensor_core_retrieval_argument_contract():
+    lib = cabi.load()
+    arch = torch.zeros(1, 2, 64, 64, device=DEV, dtype=torch.bfloat16)
+    q = torch.zeros(1, 128, 64, device=DEV, dtype=torch.bfloat16)
+    online = torch.ones(1, 128, 64, device=DEV, dtype=torch.bfloat16)
+    idx = torch.zeros(1, 128, 1, device=DEV, dtype=torch.int64)
+    gates = torch.ones(1, 128, 1, device=DEV)
+    out = torch.empty_like(online)
+    def call(S, R, H, K):
+        return lib.grmx_retrieve_fuse_tc(cabi.ptr(arch), cabi.ptr(idx), cabi.ptr(gates), cabi.ptr(q), cabi.ptr(online), None, None,
+                                         1e-5, cabi.ptr(out), 1, S, 128, R, H, K, cabi.FUSE_RESIDUAL_LN, cabi.current_stream())
+    assert call(2, 1, 64, 32) == 2 and b"grmx_retrieve_fuse" in lib.grmx_last_error()      # key dim other than 64
+    assert call(2, 1, 96, 64) == 2 and call(40, 1, 64, 64) == 2 and call(2, 9, 64, 64) == 2
+    # an index outside the ring is an empty route: the token keeps its online state and the error word says so
+    idx[0, 5, 0] = 7
+    assert call(2, 1, 64, 64) == 0
+    torch.cuda.synchronize()
+    assert cabi.device_error_word() & 1
+    cabi.check(lib.grmx_device_error_reset(cabi.current_stream()))
+    assert torch.equal(out[0, 5], online[0, 5]) and cabi.device_error_word() == 0
+
+
 @pytest.mark.parametrize("B,T,L,K,H", [(2, 1024, 256, 64, 64), (8, 2048, 512, 64, 128), (64, 2048, 128, 64, 64),
                                        (1, 4096, 512, 128, 64)])
 def test_scan_over_whole_segments_leaves_every_segment_state_in_the_archive(B, T, L, K, H):
