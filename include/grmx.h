@@ -358,6 +358,20 @@ int grmx_normalize_rows(const void* x, void* out, int64_t N, int64_t K, float ep
                         void* stream);
 
 /*
+ * Two 64-wide projections of the same input with the L2 normalisation in the epilogue, in one pass over x:
+ *   out_a[n,:] = normalize(x[n,:] W[0:64,:]^T + bias[0:64]),  out_b[n,:] = normalize(x[n,:] W[64:128,:]^T + bias[64:128])
+ * x bf16 [rows, D], weights bf16 [128, D] (the two weight matrices stacked), bias float32 [128] or NULL,
+ * out_a / out_b bf16 [rows, 64]; normalize(y) = y / max(||y||_2, eps).  One tcgen05 product per tile of 128
+ * rows with the stacked weights resident in shared memory; products accumulate in fp32 and the norm is taken
+ * of the fp32 sums.  Covers K == 64 and D a multiple of 64 up to 512, 16-byte aligned tensors;
+ * GRMX_ERR_UNSUPPORTED otherwise (project with a GEMM and call grmx_normalize_rows).
+ * Replaces F.normalize(key_proj(x)) and F.normalize(query_proj(x)) (grm/core/paper_grm.py:491-493); the
+ * reference has no native counterpart.
+ */
+int grmx_project_normalize(const void* x_bf16, const void* weights_bf16, const float* bias, void* out_a_bf16,
+                           void* out_b_bf16, int64_t rows, int64_t D, int64_t K, float eps, void* stream);
+
+/*
  * archive[b, slot, :] = memory[b, :] and, when archive_bf16 is not NULL, the same values rounded to
  * bf16 into archive_bf16[b, slot, :].  memory float32 [B,row_elems] (row_elems = H*K), archive float32
  * [B,S,row_elems], archive_bf16 bf16 [B,S,row_elems] or NULL.  One pass over the state: the bf16 ring is

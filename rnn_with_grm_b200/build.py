@@ -46,6 +46,7 @@ CUDA_SOURCES = [
     "select_fuse.cu",
     "archive_push.cu",
     "normalize_rows.cu",
+    "project_normalize.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

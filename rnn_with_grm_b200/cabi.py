@@ -92,6 +92,7 @@ SIGNATURES = {
         [c_void_p] * 7 + [c_int64] * 7 + [c_float, c_int, c_int, c_void_p],
     ),
     "grmx_normalize_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_int, c_void_p]),
+    "grmx_project_normalize": (c_int, [c_void_p] * 5 + [c_int64] * 3 + [c_float, c_void_p]),
     "grmx_archive_push": (c_int, [c_void_p] * 3 + [c_int64] * 4 + [c_void_p]),
     "grmx_device_error_word": (c_int, [POINTER(c_uint32), c_void_p]),
     "grmx_device_error_reset": (c_int, [c_void_p]),

@@ -381,6 +381,34 @@ at::Tensor l2_normalize_cuda(const at::Tensor& x, double eps, bool to_bfloat16) 
   return out;
 }
 
+// x bf16 [..., D], weights bf16 [128, D] (two stacked 64-row matrices), bias fp32 [128]? -> two bf16 [..., 64]
+std::tuple<at::Tensor, at::Tensor> project_normalize_cuda(const at::Tensor& x, const at::Tensor& weights,
+                                                          const c10::optional<at::Tensor>& bias, double eps) {
+  TORCH_CHECK(x.is_cuda() && weights.is_cuda(), "project_normalize needs CUDA tensors");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && weights.scalar_type() == at::kBFloat16, "x and weights must be bfloat16");
+  TORCH_CHECK(x.dim() >= 2 && weights.dim() == 2 && weights.size(1) == x.size(-1) && weights.size(0) % 2 == 0,
+              "weights must be [2K, D] for x [..., D]");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto in = x.contiguous();
+  auto w = weights.contiguous();
+  const int64_t D = in.size(-1), K = w.size(0) / 2;
+  const int64_t rows = in.numel() / D;
+  at::Tensor b_keep;
+  const float* b_ptr = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    b_keep = bias->to(at::kFloat).contiguous();
+    TORCH_CHECK(b_keep.numel() == 2 * K, "bias must hold 2K values");
+    b_ptr = b_keep.data_ptr<float>();
+  }
+  std::vector<int64_t> shape(in.sizes().begin(), in.sizes().end());
+  shape.back() = K;
+  auto a = at::empty(shape, in.options());
+  auto b = at::empty(shape, in.options());
+  check_status(grmx_project_normalize(in.data_ptr(), w.data_ptr(), b_ptr, a.data_ptr(), b.data_ptr(), rows, D, K,
+                                      static_cast<float>(eps), current_stream()));
+  return {a, b};
+}
+
 void archive_push_cuda(const at::Tensor& memory, at::Tensor archive, c10::optional<at::Tensor> shadow, int64_t slot) {
   TORCH_CHECK(archive.dim() == 4 && memory.dim() == 3, "memory [B, H, K] goes into archive [B, S, H, K]");
   TORCH_CHECK(memory.is_cuda() && archive.is_cuda(), "archive_push needs CUDA tensors");
@@ -518,6 +546,7 @@ TORCH_LIBRARY(grmx, m) {
   m.def("retrieve_fuse_tc(Tensor archive, Tensor indices, Tensor gates, Tensor queries, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
   m.def("chunk_scan_segments(Tensor keys, Tensor values, Tensor queries, Tensor memory, float decay, Tensor(a!) archive, int first_slot, int segment_tokens) -> (Tensor hidden, Tensor memory_out)");
   m.def("l2_normalize(Tensor x, float eps, bool to_bfloat16) -> Tensor");
+  m.def("project_normalize(Tensor x, Tensor weights, Tensor? bias, float eps) -> (Tensor a, Tensor b)");
   m.def("archive_push(Tensor memory, Tensor(a!) archive, Tensor(b!)? shadow, int slot) -> ()");
   m.def("select_fuse(Tensor states, Tensor indices, Tensor gates, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
 }
@@ -530,6 +559,7 @@ TORCH_LIBRARY_IMPL(grmx, CUDA, m) {
   m.impl("retrieve_fuse_tc", retrieve_fuse_tc_cuda);
   m.impl("select_fuse", select_fuse_cuda);
   m.impl("archive_push", archive_push_cuda);
+  m.impl("project_normalize", project_normalize_cuda);
   m.impl("l2_normalize", l2_normalize_cuda);
   m.impl("chunk_scan_segments", chunk_scan_segments_cuda);
 }

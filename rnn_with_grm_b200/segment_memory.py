@@ -239,6 +239,9 @@ class SegmentMemoryRunner:
         # and neither gathered matrices nor candidate states exist.  False: the batched GEMM over all
         # candidates followed by ``select_fuse``.
         self.tensor_core_retrieval = True
+        # key and query projections with the normalisation in the epilogue (see _keys_and_queries)
+        self.fused_projection = True
+        self._stacked_kq = None
         self._route_query_weight: Optional[Tensor] = None
         self._fp32_cache: Dict[str, Tuple[Tensor, Tensor, int]] = {}
         self._visible_cache: Dict[Tuple[int, int, str], Tensor] = {}
@@ -264,6 +267,30 @@ class SegmentMemoryRunner:
         device = memories[0].device if device is None else torch.device(device)
         self.archive = SegmentMemoryArchive(int(batch), self.capacity, self.hidden, self.key_dim, self.input_size, device)
         self.archive.set_extra_state({"groups": {int(batch): group}})
+
+    def _keys_and_queries(self, x: Tensor) -> Tuple[Tensor, Tensor]:
+        """``F.normalize(key_proj(x))`` and ``F.normalize(query_proj(x))`` (paper_grm.py:491-493).  bf16
+        activations with a 64-wide key take one pass over ``x``: both projections as one tensor-core product
+        with the normalisation in its epilogue (``torch.ops.grmx.project_normalize``); otherwise two GEMMs and
+        the one-pass normalisation kernel."""
+        wk, wq = self.p["memory_cell.key_proj.weight"], self.p["memory_cell.query_proj.weight"]
+        D = x.shape[-1]
+        if (self.fused_projection and x.is_cuda and x.dtype == torch.bfloat16 and wk.dtype == torch.bfloat16
+                and self.key_dim == 64 and D % 64 == 0 and D <= 512):
+            cached = self._stacked_kq
+            versions = (wk._version, wq._version)
+            if cached is None or cached[0] is not wk or cached[1] is not wq or cached[2] != versions:
+                bk, bq = self.p.get("memory_cell.key_proj.bias"), self.p.get("memory_cell.query_proj.bias")
+                bias = None
+                if bk is not None or bq is not None:
+                    zero = torch.zeros(self.key_dim, device=x.device)
+                    bias = torch.cat([zero if bk is None else bk.float(), zero if bq is None else bq.float()]).contiguous()
+                cached = (wk, wq, versions, torch.cat([wk, wq], dim=0).contiguous(), bias)
+                self._stacked_kq = cached
+            k, q = torch.ops.grmx.project_normalize(x, cached[3], cached[4], 1e-6)
+            return k, q
+        return (_l2_normalized(_linear(x, self.p, "memory_cell.key_proj")),
+                _l2_normalized(_linear(x, self.p, "memory_cell.query_proj")))
 
     def _fp32_param(self, name: str) -> Optional[Tensor]:
         """The parameter as the kernels read it (fp32), converted once per parameter tensor."""
@@ -451,9 +478,8 @@ class SegmentMemoryRunner:
         archive.keep_bf16_copy()
         memory = c_init.float() if c_init is not None else torch.zeros(B, self.hidden, self.key_dim, device=x.device,
                                                                        dtype=torch.float32)
-        k = _l2_normalized(_linear(x, self.p, "memory_cell.key_proj"))
+        k, q = self._keys_and_queries(x)
         v = _linear(x, self.p, "memory_cell.value_proj")
-        q = _l2_normalized(_linear(x, self.p, "memory_cell.query_proj"))
         summaries = x.reshape(B, n_seg, L, -1).mean(dim=2, dtype=torch.float32)
         route_q_weight = self._fp32_param("gating_unit.query_projection.weight")
         self._route_key_weight = self._fp32_param("gating_unit.key_projection.weight")
@@ -571,9 +597,10 @@ class SegmentMemoryRunner:
                 return list(t.unbind(0))
             return [t[:, s0:s1].contiguous() for s0, s1 in bounds]
 
-        k_seg = per_segment(_l2_normalized(_linear(x, self.p, "memory_cell.key_proj")))
+        k_all, q_all = self._keys_and_queries(x)
+        k_seg = per_segment(k_all)
         v_seg = per_segment(_linear(x, self.p, "memory_cell.value_proj"))
-        q_seg = per_segment(_l2_normalized(_linear(x, self.p, "memory_cell.query_proj")))
+        q_seg = per_segment(q_all)
         # summaries [B, n, D]: mean of the fp32 input over each segment (paper_grm.py:522-523)
         if segment_major:
             summaries = x.mean(dim=2, dtype=torch.float32).transpose(0, 1)

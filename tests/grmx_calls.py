@@ -186,6 +186,18 @@ def normalize_rows(x, eps=1e-6, out_dtype=None):
     return out
 
 
+def project_normalize(x, weights, bias=None, eps=1e-6):
+    lib = cabi.load()
+    D = x.shape[-1]
+    K = weights.shape[0] // 2
+    rows = x.numel() // D
+    a = torch.empty(*x.shape[:-1], K, device=x.device, dtype=torch.bfloat16)
+    b = torch.empty_like(a)
+    cabi.check(lib.grmx_project_normalize(cabi.ptr(x), cabi.ptr(weights), cabi.ptr(bias), cabi.ptr(a), cabi.ptr(b), rows, D, K,
+                                          float(eps), cabi.current_stream()))
+    return a, b
+
+
 def chunk_scan_fwd_segments(k, v, q, m, decay, archive, first_slot, segment_tokens):
     lib = cabi.load()
     B, T, K = k.shape

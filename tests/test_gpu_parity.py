@@ -269,6 +269,30 @@ def test_normalize_rows_matches_normalize_in_float64(N, K):
     assert rc == 2 and b"16-byte" in lib.grmx_last_error()      # GRMX_ERR_UNSUPPORTED: the caller keeps F.normalize
 
 
+@pytest.mark.parametrize("rows,D,with_bias", [(128, 64, True), (1000, 512, True), (4096 + 77, 192, False), (5, 128, True)])
+def test_project_normalize_matches_linear_then_normalize(rows, D, with_bias):
+    """Key and query projections with the normalisation in the epilogue against x W^T + b followed by
+    F.normalize in float64 (the bf16 values of x and W, fp32 bias)."""
+    rng = np.random.default_rng(71 + rows)
+    x = dev(rng.standard_normal((rows, D)).astype(np.float32), torch.bfloat16)
+    w = dev((rng.standard_normal((128, D)) / np.sqrt(D)).astype(np.float32), torch.bfloat16)
+    bias = dev(rng.standard_normal(128).astype(np.float32) * 0.1) if with_bias else None
+    a, b = gx.project_normalize(x, w, bias)
+    y = host(x).astype(np.float64) @ host(w).astype(np.float64).T + (host(bias).astype(np.float64) if with_bias else 0.0)
+    for got, want in ((a, y[:, :64]), (b, y[:, 64:])):
+        want = want / np.maximum(np.linalg.norm(want, axis=-1, keepdims=True), 1e-6)
+        close(got, want, LOWP_TOL)
+        assert float((got.float().norm(dim=-1) - 1).abs().max()) < 1e-2
+    # a zero row stays zero (norm below eps), as F.normalize leaves it
+    x[3] = 0
+    a0, _ = gx.project_normalize(x, w, None)
+    assert float(a0[3].float().abs().max()) == 0.0
+    lib = cabi.load()
+    rc = lib.grmx_project_normalize(cabi.ptr(x), cabi.ptr(w), None, cabi.ptr(a), cabi.ptr(b), rows, D, 32, 1e-6, cabi.current_stream())
+    assert rc == 2 and b"width 64" in lib.grmx_last_error()
+    assert cabi.device_error_word() == 0
+
+
 # --------------------------------------------------------------------------- routing
 
 def test_topk_route_bit_exact_against_c_oracle():
