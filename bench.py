@@ -610,6 +610,8 @@ def wide_head_scan(lib, device, hbm_peak, rows=296, T=8192, launches=3):
                                            m_out.data_ptr(), rows, T, d, d, decay, cabi.BF16, cabi.F32,
                                            cabi.PATH_AUTO, stream))
 
+    for _ in range(30):                                 # ~25 ms of the same work first: clocks settle under the load
+        scan(0, torch.cuda.current_stream().cuda_stream)
     ms = time_graph(scan, launches)
     nbytes = rows * T * (2 * (2 * d + d) + 2 * d)
     return {"rows": rows, "T": T, "d": d, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / hbm_peak,
@@ -651,6 +653,38 @@ def segment_retrieval(lib, device, hbm_peak, launches=20):
     return {"tokens": B * C, "candidates": S, "route_us": route_ms * 1e3, "route_gbs": route_bytes / route_ms / 1e6,
             "select_fuse_us": select_ms * 1e3, "select_fuse_gbs": select_bytes / select_ms / 1e6,
             "select_fuse_frac_hbm": select_bytes / select_ms / 1e6 / hbm_peak}
+
+
+def layer_retrieval_tc(lib, device, launches=6):
+    """The retrieval of one config-4 layer for all tokens at once on the tensor cores: 8 x 8192 tokens, each
+    choosing 4 of the slots archived before its segment (16 slots of 512 x 64 bf16), residual + LayerNorm."""
+    from rnn_with_grm_b200 import cabi
+
+    B, S, Q, R, H, K = CFG4["B"], 16, CFG4["T"], CFG4["top_k"], CFG4["hidden"], CFG4["K"]
+    g = torch.Generator(device=device).manual_seed(43)
+    ring = torch.randn(B, S, H, K, device=device, generator=g).to(torch.bfloat16)
+    qs = [torch.nn.functional.normalize(torch.randn(B, Q, K, device=device, generator=g), dim=-1).to(torch.bfloat16) for _ in range(3)]
+    online = [torch.randn(B, Q, H, device=device, generator=g).to(torch.bfloat16) for _ in range(3)]
+    scores = torch.randn(B, Q, S, device=device, generator=g)
+    visible = (torch.arange(Q, device=device, dtype=torch.int32) // CFG4["segment"]).to(torch.int32)
+    idx = torch.empty(B, Q, R, device=device, dtype=torch.int64)
+    gates = torch.empty(B, Q, R, device=device)
+    cabi.check(lib.grmx_topk_select(scores.data_ptr(), visible.data_ptr(), B, Q, S, R, 1.0, idx.data_ptr(), gates.data_ptr(),
+                                    torch.cuda.current_stream().cuda_stream))
+    ln_w, ln_b = torch.ones(H, device=device), torch.zeros(H, device=device)
+    out = torch.empty(B, Q, H, device=device, dtype=torch.bfloat16)
+
+    def run(i, stream):
+        cabi.check(lib.grmx_retrieve_fuse_tc(ring.data_ptr(), idx.data_ptr(), gates.data_ptr(), qs[i % 3].data_ptr(),
+                                             online[i % 3].data_ptr(), ln_w.data_ptr(), ln_b.data_ptr(), 1e-5, out.data_ptr(),
+                                             B, S, Q, R, H, K, cabi.FUSE_RESIDUAL_LN, stream))
+
+    ms = time_graph(run, launches)
+    live = int((idx >= 0).sum().item())
+    flops = 2.0 * live * H * K                       # the products a token needs: R matrices of H x K
+    nbytes = B * Q * (K * 2 + 2 * H * 2)             # q in, online in, fused out (the ring stays in L2)
+    return {"tokens": B * Q, "slots": S, "us": ms * 1e3, "useful_tflops": flops / (ms * 1e-3) / 1e12,
+            "token_gbs": nbytes / ms / 1e6}
 
 
 def config2_backward(lib, device):
@@ -723,7 +757,7 @@ def config4_model(device):
         return e0.elapsed_time(e1) / reps, eager_ms
 
     kwargs = dict(segment_length=c4["segment"], retrieval_top_k=c4["top_k"], memory_capacity_segments=16,
-                  memory_decay=c4["decay"])
+                  memory_decay=c4["decay"], memory_storage_dtype=torch.float32)
     ms, eager_ms = timed(StackedSegmentMemoryRunner(params, c4["layers"], language_model=True, **kwargs))
     torch.cuda.empty_cache()
     body = StackedSegmentMemoryRunner(params, c4["layers"], language_model=True, **kwargs)
@@ -818,6 +852,7 @@ def other_workloads(lib, device, hbm_peak):
     torch.cuda.empty_cache()
     out["cfg4_model"] = config4_model(device)
     out["cfg4_segment_retrieval"] = segment_retrieval(lib, device, hbm_peak)
+    out["cfg4_layer_retrieval_tc"] = layer_retrieval_tc(lib, device)
     torch.cuda.empty_cache()
     out.update(config3_retrieval(lib, device, hbm_peak))
     torch.cuda.empty_cache()
@@ -995,8 +1030,8 @@ def main(argv=None) -> int:
     parser.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
     parser.add_argument("--with-workspace", action="store_true",
                         help="time the two-kernel variant of the cut (piece-state kernel + scan over a caller workspace)")
-    parser.add_argument("--only", choices=["full-occupancy", "wide-head", "config4", "segment-retrieval", "config3",
-                                           "scale-out"],
+    parser.add_argument("--only", choices=["full-occupancy", "wide-head", "config4", "segment-retrieval", "layer-retrieval",
+                                           "config3", "scale-out"],
                         help="run one of the other workloads alone and print its figures (for profiling)")
     args = parser.parse_args(argv)
     args.warmup = max(args.warmup, 3)
@@ -1037,6 +1072,8 @@ def main(argv=None) -> int:
                 out = {"cfg4_model": config4_model(device)}
             elif args.only == "segment-retrieval":
                 out = {"cfg4_segment_retrieval": segment_retrieval(lib, device, peak, launches=4)}
+            elif args.only == "layer-retrieval":
+                out = {"cfg4_layer_retrieval_tc": layer_retrieval_tc(lib, device)}
             elif args.only == "config3":
                 out = config3_retrieval(lib, device, peak)
             else:

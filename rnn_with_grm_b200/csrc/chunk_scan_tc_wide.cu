@@ -65,7 +65,6 @@ constexpr int kRegsIssue = 40;
 constexpr int kRegsLaunch = 80;        // 65536 / 768, rounded down to a multiple of 8
 static_assert(512 * kRegsCompute + kStateThreads * kRegsState + 128 * kRegsIssue <= kThreads * kRegsLaunch,
               "the state group would wait for registers that nobody releases");
-constexpr int kPrefetchAhead = 2;      // chunks asked into L2 beyond the two the rings hold
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kBufCols = 192;     // buffer (c & 1) starts at column 192 * (c & 1)
 constexpr uint32_t kColA = 64;
@@ -246,24 +245,8 @@ linear_scan_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __gr
     // ===================================================================== loader: three TMA rings
     const uint32_t leader = elect_one();
     int done_q = 0, done_k = 0, done_v = 0;
-    // The rings hold two chunks, less than what has to be in flight to cover the latency of HBM at full
-    // rate.  The tiles of the chunks beyond them are asked into L2 ahead of time (a TMA prefetch needs no
-    // shared memory), so that the load into the ring finds them there.
-    auto prefetch = [&](int c) {
-      if (c >= n_chunks) return;
-      const int t0 = c * kChunk;
-      if (vb == 0) {                                       // q and k are shared by the CTAs of the row
-        tma_prefetch_3d_if(leader, &map_q, 0, t0, b);
-        tma_prefetch_3d_if(leader, &map_q, 64, t0, b);
-        tma_prefetch_3d_if(leader, &map_k, 0, t0, b);
-        tma_prefetch_3d_if(leader, &map_k, 64, t0, b);
-      }
-      tma_prefetch_3d_if(leader, &map_v, x_v, t0, b);
-    };
-    for (int c = 2; c < 2 + kPrefetchAhead; ++c) prefetch(c);
     for (int c = 0; c < n_chunks; ++c) {
       const int t0 = c * kChunk;
-      prefetch(c + 2 + kPrefetchAhead);
       if (c >= 2) GRMX_WAIT(&bar_k_free[c & 1], c / 2 - 1)
       mbar_expect_tx_if(leader, &bar_full_k[c & 1], 2 * kSub);
       tma_load_3d_if(leader, k_stage(c), &map_k, &bar_full_k[c & 1], 0, t0, b);

@@ -214,18 +214,6 @@ __device__ __forceinline__ void tma_load_3d_if(uint32_t leader, void* dst, const
       : "memory");
 }
 
-// Ask a tile into L2 (no shared memory, no barrier): the later load of the same box finds it there.
-__device__ __forceinline__ void tma_prefetch_3d_if(uint32_t leader, const CUtensorMap* map, int x, int y, int z) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred q;\n\t"
-      "setp.ne.b32 q, %4, 0;\n\t"
-      "@q cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n\t"
-      "}" ::"l"(reinterpret_cast<uint64_t>(map)),
-      "r"(x), "r"(y), "r"(z), "r"(leader)
-      : "memory");
-}
-
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 

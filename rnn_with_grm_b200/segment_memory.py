@@ -48,8 +48,13 @@ class SegmentMemoryArchive:
     the current FIFO order (0 = oldest).
     """
 
-    def __init__(self, batch: int, capacity: int, hidden: int, key_dim: int, summary_dim: int, device):
+    def __init__(self, batch: int, capacity: int, hidden: int, key_dim: int, summary_dim: int, device,
+                 storage_dtype: torch.dtype = torch.float32):
         self.capacity = int(capacity)
+        # The reference keeps archived memories and summaries in ``memory_storage_dtype`` and widens them to
+        # fp32 when it reads them (paper_grm.py:139-140, 227).  The ring itself is fp32 (the kernels read it
+        # as it is); with another storage type every value goes through that type once, on its way in.
+        self.storage_dtype = storage_dtype
         if torch.device(device).type == "cuda" and not cuda_ops.load_grm_cuda_extension():
             raise RuntimeError("the grm_cuda extension is not loaded: " +
                                str(cuda_ops.get_grm_cuda_runtime_status().get("load_error")))
@@ -95,8 +100,17 @@ class SegmentMemoryArchive:
         if self.memories_bf16 is None:
             self.memories_bf16 = self.memories.to(torch.bfloat16)
 
+    def as_stored(self, t: Tensor) -> Tensor:
+        """``t`` as it reads back from the archive: rounded through the storage type, fp32."""
+        if self.storage_dtype == torch.float32:
+            return t.float()
+        return t.to(self.storage_dtype).float()
+
     def push(self, memory: Tensor, summary: Optional[Tensor], route_key: Optional[Tensor] = None) -> None:
         slot = (self.head + self.count) % self.capacity
+        if self.storage_dtype != torch.float32:
+            memory = self.as_stored(memory)
+            summary = None if summary is None else self.as_stored(summary)
         if memory.is_cuda and memory.dtype == torch.float32:
             torch.ops.grmx.archive_push(memory, self.memories, self.memories_bf16, slot)
         else:
@@ -205,7 +219,8 @@ class SegmentMemoryRunner:
     def __init__(self, params: Dict[str, Tensor], *, segment_length: int, retrieval_top_k: int,
                  memory_capacity_segments: int, memory_decay: float = 0.97,
                  retrieval_fusion_mode: str = "residual", memory_initialization_mode: str = "checkpoint",
-                 use_layer_norm: bool = True, layer_norm_eps: float = 1e-5, temperature: float = 1.0):
+                 use_layer_norm: bool = True, layer_norm_eps: float = 1e-5, temperature: float = 1.0,
+                 memory_storage_dtype: torch.dtype = torch.float16):
         if retrieval_fusion_mode not in ("residual", "concat", "gate", "linear"):
             raise ValueError(f"Unknown retrieval_fusion_mode: {retrieval_fusion_mode}")
         self.p = params
@@ -218,6 +233,8 @@ class SegmentMemoryRunner:
         self.use_layer_norm = use_layer_norm
         self.eps = float(layer_norm_eps)
         self.temperature = float(temperature)
+        # type the archive keeps memories and summaries in; float16 is the reference's default (paper_grm.py:362)
+        self.storage_dtype = memory_storage_dtype
         self.hidden = params["memory_cell.value_proj.weight"].shape[0]
         self.key_dim = params["memory_cell.key_proj.weight"].shape[0]
         self.input_size = params["memory_cell.key_proj.weight"].shape[1]
@@ -265,7 +282,8 @@ class SegmentMemoryRunner:
             self.archive = None
             return
         device = memories[0].device if device is None else torch.device(device)
-        self.archive = SegmentMemoryArchive(int(batch), self.capacity, self.hidden, self.key_dim, self.input_size, device)
+        self.archive = SegmentMemoryArchive(int(batch), self.capacity, self.hidden, self.key_dim, self.input_size, device,
+                                            self.storage_dtype)
         self.archive.set_extra_state({"groups": {int(batch): group}})
 
     def _keys_and_queries(self, x: Tensor) -> Tuple[Tensor, Tensor]:
@@ -473,14 +491,15 @@ class SegmentMemoryRunner:
         if reset_memory:
             self.clear_memory()
         if self.archive is None:
-            self.archive = SegmentMemoryArchive(B, self.capacity, self.hidden, self.key_dim, self.input_size, x.device)
+            self.archive = SegmentMemoryArchive(B, self.capacity, self.hidden, self.key_dim, self.input_size, x.device,
+                                                self.storage_dtype)
         archive = self.archive
         archive.keep_bf16_copy()
         memory = c_init.float() if c_init is not None else torch.zeros(B, self.hidden, self.key_dim, device=x.device,
                                                                        dtype=torch.float32)
         k, q = self._keys_and_queries(x)
         v = _linear(x, self.p, "memory_cell.value_proj")
-        summaries = x.reshape(B, n_seg, L, -1).mean(dim=2, dtype=torch.float32)
+        summaries = archive.as_stored(x.reshape(B, n_seg, L, -1).mean(dim=2, dtype=torch.float32))
         route_q_weight = self._fp32_param("gating_unit.query_projection.weight")
         self._route_key_weight = self._fp32_param("gating_unit.key_projection.weight")
         fold = self.fold_routing_projection and self.input_size <= 2 * self.route_dim
@@ -492,6 +511,8 @@ class SegmentMemoryRunner:
             raise RuntimeError("the archive cannot take the segments of this call without evicting")
         hidden, memory = torch.ops.grmx.chunk_scan_segments(k, v, q, memory, self.decay, archive.memories, first, L)
         archive.note_pushed(n_seg)
+        if archive.storage_dtype != torch.float32:      # the states the scan left in the ring, as the archive stores them
+            archive.memories[:, first:first + n_seg] = archive.as_stored(archive.memories[:, first:first + n_seg])
         archive.memories_bf16[:, first:first + n_seg].copy_(archive.memories[:, first:first + n_seg])
         held = first + n_seg
         routes = []
@@ -580,7 +601,7 @@ class SegmentMemoryRunner:
             self.clear_memory()
         if self.archive is None:
             self.archive = SegmentMemoryArchive(B, self.capacity, self.hidden, self.key_dim, self.input_size,
-                                                x.device)
+                                                x.device, self.storage_dtype)
         archive = self.archive
         if x.dtype == torch.bfloat16 and self.dense_retrieval:
             archive.keep_bf16_copy()
@@ -608,6 +629,7 @@ class SegmentMemoryRunner:
             summaries = torch.stack([x[:, s0:s1].mean(dim=1, dtype=torch.float32) for s0, s1 in bounds], dim=1)
         else:
             summaries = x.new_zeros(B, 0, x.shape[-1], dtype=torch.float32)
+        summaries = archive.as_stored(summaries)
         summary_seg = [summaries[:, i] for i in range(len(bounds))]
         # The routing keys of this call's segments are projected once, here, and archived with them
         # (the reference projects the archived summaries again in every segment, paper_grm.py:566-570;

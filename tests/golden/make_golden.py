@@ -22,6 +22,8 @@ reference's Python implementation on CPU in float32:
 * ``fusion_cfg3_*.npz``   -- ``RetrievedStateFusion(64, mode)`` as the retrieval configuration builds it
                              (``torch.manual_seed(0)``, default initialisation): weights, a few input rows
                              and the module's outputs on them.
+* ``model_cfg1_fp16_archive.npz`` -- the outputs of the same model with the reference's default float16
+                             archive storage (weights and inputs are those of ``model_cfg1.npz``).
 * ``model_fusion_*.npz``  -- the same model class, smaller (hidden 64, key dim 32, segment 64, four
                              segments), with ``retrieval_fusion_mode`` concat / gate / linear:
                              weights, inputs, outputs and final state.
@@ -221,6 +223,25 @@ def model_cfg1_case():
     )
 
 
+def model_cfg1_fp16_archive_case():
+    """Config 1 with the reference's DEFAULT archive storage type (float16, grm/core/paper_grm.py:362,139): the
+    same seed gives the same weights and inputs as model_cfg1.npz, so only the outputs are stored."""
+    from grm.core.paper_grm import SegmentRecurrentMemoryModel
+
+    torch.manual_seed(0)
+    model = SegmentRecurrentMemoryModel(
+        input_size=2, hidden_size=128, output_size=1, segment_length=128, memory_key_dim=64,
+        retrieval_top_k=2, memory_capacity_segments=8, recomputation_ratio=0.0, dropout=0.0,
+        cuda_cpp_debug_fallback=True,
+    ).eval()
+    assert model.memory_bank.memory_storage_dtype == torch.float16
+    x = adding_problem_inputs(2, 512, seed=0)
+    with torch.no_grad():
+        outputs, h_final, memory_final, aux = model(x, reset_memory=True)
+    np.savez_compressed(HERE / "model_cfg1_fp16_archive.npz", outputs=outputs.numpy(), h_final=h_final.numpy(),
+                        memory_final=memory_final.numpy())
+
+
 def model_fusion_cases():
     """The single-layer model with each weight-bearing fusion rule, small enough to keep the weights in
     the fixture."""
@@ -302,6 +323,9 @@ def main(argv=None) -> int:
     if args.only == "model_fusion":
         model_fusion_cases()
         return 0
+    if args.only == "model_cfg1_fp16_archive":
+        model_cfg1_fp16_archive_case()
+        return 0
     if args.only == "fusion_cfg3":
         fusion_cfg3_cases()
         return 0
@@ -315,6 +339,7 @@ def main(argv=None) -> int:
     fusion_cases()
     fusion_cfg3_cases()
     model_cfg1_case()
+    model_cfg1_fp16_archive_case()
     model_fusion_cases()
     total = sum(p.stat().st_size for p in HERE.glob("*.npz"))
     print(f"wrote {len(list(HERE.glob('*.npz')))} fixtures, {total / 1024:.0f} KiB")

@@ -196,7 +196,7 @@ def test_runner_with_weight_bearing_fusion_rules_matches_reference_model(golden,
     x = torch.from_numpy(g["x"]).to(DEV)
     for dense in (True, False):                                         # both retrieval forms feed the rule
         runner = SegmentMemoryRunner(params, segment_length=64, retrieval_top_k=2, memory_capacity_segments=8,
-                                     memory_decay=0.97, retrieval_fusion_mode=mode)
+                                     memory_decay=0.97, retrieval_fusion_mode=mode, memory_storage_dtype=torch.float32)
         runner.dense_retrieval = dense
         out, h_final, memory, aux = runner.forward(x, reset_memory=True)
         assert aux["num_segments"] == int(g["num_segments"]) == 4

@@ -18,7 +18,8 @@ FP32_TOL = 1e-5
 
 def _runner(g, **overrides):
     params = {k[len("param::"):]: torch.from_numpy(v).to(DEV) for k, v in g.items() if k.startswith("param::")}
-    kwargs = dict(segment_length=128, retrieval_top_k=2, memory_capacity_segments=8, memory_decay=0.97)
+    kwargs = dict(segment_length=128, retrieval_top_k=2, memory_capacity_segments=8, memory_decay=0.97,
+                  memory_storage_dtype=torch.float32)
     kwargs.update(overrides)
     return SegmentMemoryRunner(params, **kwargs)
 
@@ -43,6 +44,26 @@ def test_single_layer_model_matches_reference_forward(golden):
     # a second call without reset sees the first call's segments (paper_grm.py:663-664)
     _, _, _, aux2 = runner.forward(x, reset_memory=False)
     assert aux2["num_segments"] == 8 and aux2["total_pushed"] == 8
+
+
+def test_default_float16_archive_storage_matches_reference_default(golden):
+    """The reference archives memories and summaries in float16 unless told otherwise (paper_grm.py:362,
+    139-140) and widens them when it retrieves; a runner built without ``memory_storage_dtype`` does the
+    same.  Rounding the archived states to float16 turns last-bit differences between two fp32
+    implementations into an occasional whole float16 step (1e-3 of a value) in an archived element, so the
+    two agree to about 1e-5 .. 1e-4 here instead of 1e-5; the difference from float32 storage is 5e-4."""
+    g, want = golden("model_cfg1"), golden("model_cfg1_fp16_archive")
+    params = {k[len("param::"):]: torch.from_numpy(v).to(DEV) for k, v in g.items() if k.startswith("param::")}
+    runner = SegmentMemoryRunner(params, segment_length=128, retrieval_top_k=2, memory_capacity_segments=8, memory_decay=0.97)
+    assert runner.storage_dtype == torch.float16
+    x = torch.from_numpy(g["x"]).to(DEV)
+    out, h_final, memory, _ = runner.forward(x, reset_memory=True)
+    assert go.rel_err(out.cpu().numpy(), want["outputs"]) < 5e-5
+    assert go.rel_err(h_final.cpu().numpy(), want["h_final"]) < 5e-5
+    assert go.rel_err(memory.cpu().numpy(), want["memory_final"]) < FP32_TOL      # the carried state is never rounded
+    assert go.rel_err(out.cpu().numpy(), g["outputs"]) > 2e-4
+    assert runner.archive.memories.dtype == torch.float32
+    assert torch.equal(runner.archive.memories[:, :4], runner.archive.memories[:, :4].half().float())
 
 
 def test_graph_replay_of_the_forward_pass_matches_eager(golden):
@@ -151,7 +172,7 @@ def _cfg4_runner(g, dtype):
     if dtype != torch.float32:
         params = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in params.items()}
     runner = StackedSegmentMemoryRunner(params, 4, language_model=True, segment_length=512, retrieval_top_k=4,
-                                        memory_capacity_segments=16, memory_decay=0.97)
+                                        memory_capacity_segments=16, memory_decay=0.97, memory_storage_dtype=torch.float32)
     return runner, zipf_token_ids(8, 8192, 32768, 1.1, seed=0).to(DEV)
 
 
@@ -194,7 +215,7 @@ def test_whole_sequence_form_equals_the_segment_loop(golden):
     x = torch.from_numpy(g["x"]).to(DEV).to(torch.bfloat16)
     def runner(fuse, **kw):
         r = SegmentMemoryRunner(params, segment_length=128, retrieval_top_k=2, memory_capacity_segments=8,
-                                memory_decay=0.97, **kw)
+                                memory_decay=0.97, memory_storage_dtype=torch.float32, **kw)
         r.fuse_segments = fuse
         return r
     whole, loop = runner(True), runner(False)
@@ -244,7 +265,7 @@ def test_whole_sequence_form_with_the_other_fusion_rules(golden, mode):
     outs = []
     for fuse in (True, False):
         r = SegmentMemoryRunner(params, segment_length=128, retrieval_top_k=2, memory_capacity_segments=8,
-                                memory_decay=0.97, retrieval_fusion_mode=mode)
+                                memory_decay=0.97, retrieval_fusion_mode=mode, memory_storage_dtype=torch.float32)
         r.fuse_segments = fuse
         outs.append(r.forward(x, reset_memory=True)[0].float().cpu().numpy())
     assert go.rel_err(outs[0], outs[1]) < 2e-2
