@@ -1033,6 +1033,10 @@ def main(argv=None) -> int:
     parser.add_argument("--only", choices=["full-occupancy", "wide-head", "config4", "segment-retrieval", "layer-retrieval",
                                            "config3", "scale-out"],
                         help="run one of the other workloads alone and print its figures (for profiling)")
+    # earlier spellings of --only, kept so that the commands recorded under profiles/ still run as written
+    for old, new in (("--full-occupancy-only", "full-occupancy"), ("--config4-only", "config4"),
+                     ("--segment-retrieval-only", "segment-retrieval")):
+        parser.add_argument(old, dest="only", action="store_const", const=new, help=argparse.SUPPRESS)
     args = parser.parse_args(argv)
     args.warmup = max(args.warmup, 3)
     args.steps = max(args.steps, 1)
