@@ -51,17 +51,17 @@ def test_default_float16_archive_storage_matches_reference_default(golden):
     139-140) and widens them when it retrieves; a runner built without ``memory_storage_dtype`` does the
     same.  Rounding the archived states to float16 turns last-bit differences between two fp32
     implementations into an occasional whole float16 step (1e-3 of a value) in an archived element, so the
-    two agree to about 1e-5 .. 1e-4 here instead of 1e-5; the difference from float32 storage is 5e-4."""
+    two agree to 1e-5 .. 1e-4 here (tested at 2e-4) instead of 1e-5; float32 storage differs by 5e-4."""
     g, want = golden("model_cfg1"), golden("model_cfg1_fp16_archive")
     params = {k[len("param::"):]: torch.from_numpy(v).to(DEV) for k, v in g.items() if k.startswith("param::")}
     runner = SegmentMemoryRunner(params, segment_length=128, retrieval_top_k=2, memory_capacity_segments=8, memory_decay=0.97)
     assert runner.storage_dtype == torch.float16
     x = torch.from_numpy(g["x"]).to(DEV)
     out, h_final, memory, _ = runner.forward(x, reset_memory=True)
-    assert go.rel_err(out.cpu().numpy(), want["outputs"]) < 5e-5
-    assert go.rel_err(h_final.cpu().numpy(), want["h_final"]) < 5e-5
+    assert go.rel_err(out.cpu().numpy(), want["outputs"]) < 2e-4
+    assert go.rel_err(h_final.cpu().numpy(), want["h_final"]) < 2e-4
     assert go.rel_err(memory.cpu().numpy(), want["memory_final"]) < FP32_TOL      # the carried state is never rounded
-    assert go.rel_err(out.cpu().numpy(), g["outputs"]) > 2e-4
+    assert go.rel_err(out.cpu().numpy(), g["outputs"]) > 3e-4
     assert runner.archive.memories.dtype == torch.float32
     assert torch.equal(runner.archive.memories[:, :4], runner.archive.memories[:, :4].half().float())
 
