@@ -38,6 +38,7 @@ CUDA_SOURCES = [
     "chunk_scan_tc_pipe.cu",
     "chunk_scan_tc_split.cu",
     "chunk_scan_tc_wide.cu",
+    "chunk_scan_tc_square.cu",
     "apply_query.cu",
     "gather.cu",
     "topk_route.cu",

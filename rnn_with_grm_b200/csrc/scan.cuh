@@ -61,6 +61,11 @@ int launch_scan_tcgen05_pipe(const ScanParams& p, const SplitInfo& split, cudaSt
 bool scan_tcgen05_wide_supported(const ScanParams& p);
 int launch_scan_tcgen05_wide(const ScanParams& p, cudaStream_t stream);
 
+// Heads of d_k = 128 whose value width is a multiple of 128: one CTA per (row, 128 value features), so
+// that q and k tiles also cross from L2 to the SMs once.  Forward scans only.
+bool scan_tcgen05_square_supported(const ScanParams& p);
+int launch_scan_tcgen05_square(const ScanParams& p, cudaStream_t stream);
+
 // Cutting along T: bytes of scratch the cut needs for this call (0 when a cut would not help or
 // the shape is not covered), and the launch that runs the piece-state kernel followed by the scan.
 int64_t scan_tcgen05_split_scratch_bytes(const ScanParams& p, int sm_count = 0);   // 0: the current device

@@ -170,6 +170,7 @@ bool scan_tcgen05_supported(const ScanParams& p, int io_dtype, int state_dtype, 
 }
 
 int launch_scan_tcgen05(const ScanParams& p, cudaStream_t stream) {
+  if (scan_tcgen05_square_supported(p)) return launch_scan_tcgen05_square(p, stream);
   if (scan_tcgen05_wide_supported(p)) return launch_scan_tcgen05_wide(p, stream);
   return launch_scan_tcgen05_selfcut(p, stream);
 }

@@ -652,10 +652,13 @@ def test_tcgen05_backward_through_three_scans():
 
 
 @pytest.mark.parametrize("B,T,K,H", [(2, 300, 64, 128), (2, 512, 128, 128), (1, 640, 64, 512), (3, 256, 128, 64),
-                                     (150, 256, 128, 128), (2, 1024, 192, 64)])
+                                     (150, 256, 128, 128), (2, 1024, 192, 64), (2, 300, 128, 256), (1, 130, 128, 128),
+                                     (2, 1000, 128, 192), (3, 1, 128, 128), (2, 2048, 128, 128)])
 def test_tcgen05_scan_wide_heads_run_as_blocks(B, T, K, H):
     """Heads wider than 64 are scanned as 64 x 64 blocks of the state; the outputs of the key/query
-    blocks are summed in the bf16 output (one more rounding per block), the state is exact per block."""
+    blocks are summed in the bf16 output (one more rounding per block), the state is exact per block.
+    Forward scans with d_k = 128 take the one-pass kernels instead: one CTA per row and 128 value features
+    when d_v is a multiple of 128, per 64 value features otherwise."""
     k, v, q, m = make_chunk(K + H + T, B, T, K, H)
     tk, tv, tq = dev(k, torch.bfloat16), dev(v, torch.bfloat16), dev(q, torch.bfloat16)
     want_h, want_m = go.chunk_update_sequential(host(tk), host(tv), host(tq), m, 0.97)
