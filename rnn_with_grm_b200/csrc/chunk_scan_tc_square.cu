@@ -25,7 +25,7 @@
 // (grm/csrc/chunk_update.cu:17,508).
 //
 // Roles (20 warps, registers re-divided between them at entry):
-//   warp 16      issuer A: S_c; owns the TMEM allocation
+//   warp 16      issuer A: S_c, then the store of out_{c-1}; owns the TMEM allocation
 //   warp 17      issuer B: U^T_c
 //   warp 18      issuer C: R_c, then A_c
 //   warp 19      loader: q and k rings of two stages, one v stage
@@ -120,9 +120,9 @@ linear_scan_tc_square_kernel(const __grid_constant__ CUtensorMap map_q, const __
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBars);
   uint64_t* bar_full_q = bars;            // [2] TMA bytes landed                                         (1 + tx)
   uint64_t* bar_full_k = bars + 2;        // [2]
-  uint64_t* bar_q_free = bars + 4;        // [2] S_c, R_c complete and both halves of out_c stored        (2 commits + 2)
+  uint64_t* bar_q_free = bars + 4;        // [2] S_c, R_c complete and out_c read by its store            (2 commits + 1)
   uint64_t* bar_k_free = bars + 6;        // [2] S_c and U_c complete                                     (2 commits)
-  uint64_t* bar_out_ready = bars + 8;     // [2] compute group h has written its half of out_c            (128)
+  uint64_t* bar_out_ready = bars + 8;     //     the compute groups have written out_c                    (256)
   uint64_t* bar_full_v = bars + 10;       //     v_c landed                                               (1 + tx)
   uint64_t* bar_v_free = bars + 11;       //     A_c complete and Vw_c copied                             (1 commit + 256)
   uint64_t* bar_s_done = bars + 12;       //     S_c complete                                             (commit)
@@ -159,10 +159,10 @@ linear_scan_tc_square_kernel(const __grid_constant__ CUtensorMap map_q, const __
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_full_q[i], 1);
       mbar_init(&bar_full_k[i], 1);
-      mbar_init(&bar_q_free[i], 4);
+      mbar_init(&bar_q_free[i], 3);
       mbar_init(&bar_k_free[i], 2);
-      mbar_init(&bar_out_ready[i], 128);
     }
+    mbar_init(bar_out_ready, kComputeThreads);
     mbar_init(bar_full_v, 1);
     mbar_init(bar_v_free, 1 + kStateThreads);
     mbar_init(bar_s_done, 1);
@@ -203,6 +203,19 @@ linear_scan_tc_square_kernel(const __grid_constant__ CUtensorMap map_q, const __
   uint8_t* const vw_tile = smem + kOffVw;
   uint8_t* const mb_tile = smem + kOffMb;
 
+  // out_c leaves from the q stage it was staged in (rows beyond T are clipped by the store); the stage
+  // goes back to the loader when the store has read it
+  auto store_out = [&](int c, uint32_t leader) {
+    if (leader) {
+      tma_store_3d(q_stage(c), &map_o, x_v, c * kChunk, b);
+      tma_store_3d(q_stage(c) + kSub, &map_o, x_v + 64, c * kChunk, b);
+      bulk_commit();
+      bulk_wait_read();
+      mbar_arrive(&bar_q_free[c & 1]);
+    }
+    __syncwarp();
+  };
+
 #define GRMX_WAIT(bar, phase)                                        \
   if (!mbar_wait((bar), static_cast<uint32_t>(phase) & 1u, s_abort)) \
     break;
@@ -214,7 +227,7 @@ linear_scan_tc_square_kernel(const __grid_constant__ CUtensorMap map_q, const __
   //   loader:   k(c) needs k_free(c-2) = S_{c-2} and U_{c-2} retired; q(c) needs q_free(c-2) = S_{c-2}, R_{c-2}
   //             retired and out_{c-2} read by its stores; v(c) needs v_free(c-1) = A_{c-1} retired and
   //             Vw_{c-1} copied
-  //   issuer A: S_c needs full_q(c), full_k(c), a_done(c-1)
+  //   issuer A: S_c needs full_q(c), full_k(c), a_done(c-1); the store of out_{c-1} needs out_ready(c-1)
   //   issuer B: U_c needs vw_ready(c), full_k(c), u_free(c-1)
   //   issuer C: R_c needs mb_ready(c), full_q(c), ra_free(c-1); A_c needs p_ready(c) and full_v(c)
   //   state:    Vw_c needs full_v(c) and u_done(c-1) (waited for in the iteration before); M_c needs
@@ -240,6 +253,15 @@ linear_scan_tc_square_kernel(const __grid_constant__ CUtensorMap map_q, const __
       tc_commit_if(leader, bar_s_done);
       tc_commit_if(leader, &bar_q_free[c & 1]);
       tc_commit_if(leader, &bar_k_free[c & 1]);
+      // out_{c-1} is being written while S_c runs: store it from here, where waiting until the store has
+      // read its source delays nothing (a compute warp that waited would be late for the next P pass)
+      if (c >= 1) {
+        GRMX_WAIT(bar_out_ready, c - 1)
+        store_out(c - 1, leader);
+      }
+    }
+    if (!*s_abort && mbar_wait(bar_out_ready, static_cast<uint32_t>(n_chunks - 1) & 1u, s_abort)) {
+      store_out(n_chunks - 1, leader);
     }
   } else if (warp == kLoader) {
     // ===================================================================== loader
@@ -420,7 +442,6 @@ linear_scan_tc_square_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int quarter = warp & 3;
     const int row = tid & 127;                // token row within the chunk == TMEM lane
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    int stores_pending = -1;                  // chunk whose store by this thread has not been waited for yet
 
     for (int c = 0; c < n_chunks; ++c) {
       // ---- S_c -> P_c: group g turns the 32-column blocks 2g and 2g+1 of S into P ----
@@ -463,16 +484,10 @@ linear_scan_tc_square_kernel(const __grid_constant__ CUtensorMap map_q, const __
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p_ready);
-      // the store of the chunk before has read its tile by now: the q stage goes back to the loader
-      if (row == 0 && stores_pending >= 0) {
-        bulk_wait_read();
-        mbar_arrive(&bar_q_free[stores_pending & 1]);
-        stores_pending = -1;
-      }
 
       // ---- out_c: group g writes columns 64g .. 64g+63, i.e. sub-tile g of the q stage of this chunk,
-      //      which S_c and R_c have finished with; out_i = hs * decay^(i+1) R_i + A_i -> bf16 -> one TMA
-      //      store per sub-tile (rows beyond T are clipped by the store) ----
+      //      which S_c and R_c have finished with; out_i = hs * decay^(i+1) R_i + A_i -> bf16; issuer A
+      //      stores the tile ----
       GRMX_WAIT(bar_r_done, c)
       GRMX_WAIT(bar_a_done, c)
       tc_fence_after();
@@ -505,15 +520,8 @@ linear_scan_tc_square_kernel(const __grid_constant__ CUtensorMap map_q, const __
         }
       }
       fence_proxy_async();
-      mbar_arrive(&bar_out_ready[g]);
-      if (row == 0) {
-        GRMX_WAIT(&bar_out_ready[g], c)
-        tma_store_3d(q_stage(c) + g * kSub, &map_o, x_v + 64 * g, c * kChunk, b);
-        bulk_commit();
-        stores_pending = c;
-      }
+      mbar_arrive(bar_out_ready);
     }
-    if (row == 0) bulk_wait_read();   // the last store still reads shared memory
   }
 #undef GRMX_WAIT
 
