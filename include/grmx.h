@@ -310,6 +310,27 @@ int grmx_retrieve_fuse(const float* archive, const int64_t* indices, const float
                        int64_t Q, int64_t R, int64_t H, int64_t K, int mode, void* stream);
 
 /*
+ * The slot-major form of grmx_retrieve_fuse (modes GRMX_FUSE_CONTRIB and GRMX_FUSE_RESIDUAL_LN): one
+ * CTA per batch row reads every chosen matrix once and applies it to all queries of the row that chose
+ * it, where the query-major form reads a matrix once per query.  Same tensors and semantics; the sum
+ * over a query's routes runs in slot order instead of route order, so results agree with
+ * grmx_retrieve_fuse to fp32 rounding, not bit for bit.  Covers K a multiple of 32 up to 256, H up to 256
+ * with 1, 2, 4 or 8 blocks of 32 rows, and rows whose queries and sums fit in shared memory beside eight
+ * blocks of 32 matrix rows (200 KiB in all); GRMX_ERR_UNSUPPORTED otherwise.
+ * grmx_retrieve_fuse takes this form by itself when B >= 64 and Q * R >= 2 * S (a row's queries share
+ * matrices and there are rows enough to fill the GPU); GRMX_RETRIEVE_ROWS=off in the environment keeps
+ * it on the query-major kernel.
+ *
+ * Replaces the same chain as grmx_retrieve_fuse for segment-level routing
+ * (grm/core/paper_grm.py:566-611): every segment query of a row chooses among the same archived
+ * matrices of that row (grm/csrc/batched_gather.cu:38-41 indexes within a batch row).
+ */
+int grmx_retrieve_fuse_rows(const float* archive, const int64_t* indices, const float* gates,
+                            const float* queries, const float* online, const float* ln_weight,
+                            const float* ln_bias, float ln_eps, void* out, int64_t B, int64_t S,
+                            int64_t Q, int64_t R, int64_t H, int64_t K, int mode, void* stream);
+
+/*
  * grmx_retrieve_fuse for per-token routing on the tensor cores: every token of a batch row chooses R of
  * the row's S archived matrices, all in bf16 (archive_bf16 [B,S,H,K], queries_bf16 [B,Q,K], online_bf16 and
  * out_bf16 [B,Q,H]; indices int64 and gates float32 [B,Q,R] as in grmx_retrieve_fuse).  For a tile of 128

@@ -79,6 +79,10 @@ SIGNATURES = {
         c_int,
         [c_void_p] * 7 + [c_float, c_void_p] + [c_int64] * 6 + [c_int, c_void_p],
     ),
+    "grmx_retrieve_fuse_rows": (
+        c_int,
+        [c_void_p] * 7 + [c_float, c_void_p] + [c_int64] * 6 + [c_int, c_void_p],
+    ),
     "grmx_retrieve_fuse_tc": (
         c_int,
         [c_void_p] * 7 + [c_float, c_void_p] + [c_int64] * 6 + [c_int, c_void_p],

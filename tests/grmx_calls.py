@@ -144,6 +144,19 @@ def retrieve_fuse(archive, indices, gates, queries, online=None, ln_weight=None,
     return out
 
 
+def retrieve_fuse_rows(archive, indices, gates, queries, online=None, ln_weight=None, ln_bias=None, eps=1e-5,
+                       mode=cabi.FUSE_RESIDUAL_LN):
+    """The slot-major form, asked for by name (grmx_retrieve_fuse picks it by shape)."""
+    lib = cabi.load()
+    B, S, H, K = archive.shape
+    _, Q, R = indices.shape
+    out = torch.empty(B, Q, H, device=archive.device, dtype=torch.float32)
+    cabi.check(lib.grmx_retrieve_fuse_rows(cabi.ptr(archive), cabi.ptr(indices), cabi.ptr(gates), cabi.ptr(queries),
+                                           cabi.ptr(online), cabi.ptr(ln_weight), cabi.ptr(ln_bias), float(eps),
+                                           cabi.ptr(out), B, S, Q, R, H, K, mode, cabi.current_stream()))
+    return out
+
+
 def retrieve_fuse_tc(archive, indices, gates, queries, online=None, ln_weight=None, ln_bias=None, eps=1e-5,
                      mode=cabi.FUSE_RESIDUAL_LN):
     """Tensor-core retrieval: bf16 archive, queries, online state and output."""

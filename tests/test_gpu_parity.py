@@ -411,6 +411,55 @@ def test_retrieve_fuse_modes(H, K):
     close(got, go.retrieve_fuse(archive, idx, gates, queries, online), FP32_TOL)
 
 
+@pytest.mark.parametrize("B,S,Q,R,H,K", [(3, 9, 5, 4, 64, 64), (2, 32, 32, 8, 128, 128), (70, 32, 32, 4, 64, 64),
+                                         (2, 5, 7, 3, 20, 32), (1, 40, 3, 2, 100, 96), (2, 6, 1, 6, 33, 160),
+                                         (2, 3, 40, 2, 256, 32), (3, 17, 9, 5, 1, 64)])
+def test_retrieve_fuse_slot_major_form(B, S, Q, R, H, K):
+    """One CTA per batch row that reads every chosen matrix once: same results as the query-major kernel
+    to fp32 rounding (the sum over a query's routes runs in slot order), empty routes, repeated slots and
+    queries without any route included."""
+    rng = np.random.default_rng(B + S + Q + R + H + K)
+    archive = rng.standard_normal((B, S, H, K)).astype(np.float32)
+    idx = rng.integers(0, S, size=(B, Q, R))
+    idx[0, 0, :] = -1                                   # nothing to retrieve
+    idx[B - 1, Q - 1, R - 1] = -1                       # one empty route
+    if R >= 2:
+        idx[0, Q - 1, 1] = idx[0, Q - 1, 0]             # the same slot twice
+    gates = rng.random((B, Q, R)).astype(np.float32)
+    queries = rng.standard_normal((B, Q, K)).astype(np.float32)
+    online = rng.standard_normal((B, Q, H)).astype(np.float32)
+    w = rng.uniform(0.5, 1.5, H).astype(np.float32)
+    b = rng.uniform(-0.5, 0.5, H).astype(np.float32)
+    t = dict(archive=dev(archive), indices=dev(idx), gates=dev(gates), queries=dev(queries))
+    got = gx.retrieve_fuse_rows(**t, mode=cabi.FUSE_CONTRIB)
+    close(got, go.retrieve_fuse(archive, idx, gates, queries, mode="contrib"), FP32_TOL)
+    got = gx.retrieve_fuse_rows(**t, online=dev(online), ln_weight=dev(w), ln_bias=dev(b))
+    close(got, go.retrieve_fuse(archive, idx, gates, queries, online, w, b), FP32_TOL)
+    assert torch.equal(got[0, 0], dev(online)[0, 0])    # no archived segment: online passes through
+    got = gx.retrieve_fuse_rows(**t, online=dev(online))
+    close(got, go.retrieve_fuse(archive, idx, gates, queries, online), FP32_TOL)
+    assert cabi.device_error_word() == 0
+
+
+def test_retrieve_fuse_slot_major_form_limits():
+    lib = cabi.load()
+    a = torch.zeros(1, 2, 8, 48, device=DEV)            # K = 48 is not a multiple of 32
+    i = torch.zeros(1, 1, 1, device=DEV, dtype=torch.int64)
+    g = torch.ones(1, 1, 1, device=DEV)
+    q = torch.zeros(1, 1, 48, device=DEV)
+    o = torch.zeros(1, 1, 8, device=DEV)
+    rc = lib.grmx_retrieve_fuse_rows(cabi.ptr(a), cabi.ptr(i), cabi.ptr(g), cabi.ptr(q), None, None, None, 1e-5,
+                                     cabi.ptr(o), 1, 2, 1, 1, 8, 48, cabi.FUSE_CONTRIB, cabi.current_stream())
+    assert rc == 2 and b"multiple of 32" in lib.grmx_last_error()
+    # an index beyond the archive sets the error word and is skipped, as in the query-major kernel
+    a = torch.ones(1, 2, 8, 32, device=DEV)
+    i = torch.tensor([[[5]]], device=DEV, dtype=torch.int64)
+    q = torch.ones(1, 1, 32, device=DEV)
+    out = gx.retrieve_fuse_rows(a, i, g, q, mode=cabi.FUSE_CONTRIB)
+    assert float(out.abs().sum()) == 0.0 and cabi.device_error_word() == 1
+    cabi.check(lib.grmx_device_error_reset(cabi.current_stream()))
+
+
 def test_retrieve_fuse_equals_gather_then_apply(golden):
     rng = np.random.default_rng(51)
     B, S, Q, R, H, K = 2, 6, 4, 3, 64, 64
