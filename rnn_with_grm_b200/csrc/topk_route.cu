@@ -107,6 +107,59 @@ __host__ __device__ constexpr size_t few_keys_smem_bytes(int D, int queries_per_
   return sizeof(float) * ((size_t)D * kFewKeys + (size_t)queries_per_cta * (D + kFewPad));
 }
 
+// Selection for the few-keys kernels: lane (half, s) holds the score of key s for the query of its half-warp
+// (two queries per warp at once).  The rank of a key among the visible ones (how many beat it: higher score,
+// or the same score and a lower index) comes from 16 independent shuffles instead of a round of dependent
+// ones per route; the key of rank r is route r.  All 32 lanes must call it together.
+__device__ __forceinline__ void few_keys_select(float score, int lane, int64_t b, int64_t q, int64_t Q, int S, bool query_live,
+                                                const int32_t* __restrict__ visible, int top_k, float temperature,
+                                                int64_t* __restrict__ indices_out, float* __restrict__ gates_out,
+                                                float* __restrict__ scores_out) {
+  const int half = lane >> 4;
+  const int s = lane & (kFewKeys - 1);
+  if (scores_out != nullptr && query_live && s < S) scores_out[(b * Q + q) * S + s] = score;
+  int n_vis = S;
+  if (visible != nullptr && query_live) {
+    n_vis = visible[q];
+    n_vis = n_vis < 0 ? 0 : (n_vis > S ? S : n_vis);
+  }
+  const int R = top_k < n_vis ? top_k : n_vis;
+  const bool seen = s < n_vis;
+  const unsigned long long mine =
+      seen ? (((unsigned long long)ordered_bits(score) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)s)) : 0ull;
+  int rank = 0;
+#pragma unroll
+  for (int j = 0; j < kFewKeys; ++j) {
+    const unsigned long long other = __shfl_sync(0xffffffffu, mine, (lane & 16) | j);
+    rank += other > mine ? 1 : 0;
+  }
+  if (R == n_vis) rank = s;                                  // every visible key is taken: identity order
+  const bool chosen = seen && rank < R;
+  // softmax over the chosen scores, inside the half-warp
+  const float x = chosen ? score / temperature : -CUDART_INF_F;
+  float mx = x;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  // fmaxf drops NaN; put it back so a NaN score poisons the row as softmax does
+  const unsigned nan_mask = __ballot_sync(0xffffffffu, chosen && x != x) & (half ? 0xffff0000u : 0x0000ffffu);
+  const float e = chosen ? expf(x - mx) : 0.0f;
+  float sum = e;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (query_live) {
+    int64_t* idx_row = indices_out + (b * Q + q) * top_k;
+    float* gate_row = gates_out + (b * Q + q) * top_k;
+    if (chosen) {
+      idx_row[rank] = s;
+      gate_row[rank] = nan_mask != 0u ? CUDART_NAN_F : e / sum;
+    }
+    for (int r = R + s; r < top_k; r += kFewKeys) {          // slots without a route
+      idx_row[r] = -1;
+      gate_row[r] = 0.0f;
+    }
+  }
+}
+
 // kFewChains queries per half-warp, kFewWarps warps per CTA; TQ: the queries as stored, float or
 // bf16 (widened while they are staged, which is exact: the scores do not depend on it)
 template <int kFewChains, int kFewWarps, typename TQ>
@@ -217,57 +270,149 @@ topk_route_few_keys_kernel(const TQ* __restrict__ queries, const float* __restri
       }
     }
   }
-  // Selection in registers, both queries of the warp at once: lane (half, s) holds the score of key s
-  // for the query of its half.  The rank of a key among the visible ones (how many beat it: higher
-  // score, or the same score and a lower index) comes from 16 independent shuffles instead of a
-  // round of dependent ones per route; the key of rank r is route r.
+  // selection in registers, both queries of the warp at once
 #pragma unroll
   for (int c = 0; c < kFewChains; ++c) {
     const int slot = warp * kFewPerWarp + half * kFewChains + c;
     const int64_t q = q0 + slot;
-    const bool query_live = q < Q;
-    const float score = acc[c] * scale;
-    if (scores_out != nullptr && query_live && s < S) scores_out[(b * Q + q) * S + s] = score;
-    int n_vis = S;
-    if (visible != nullptr && query_live) {
-      n_vis = visible[q];
-      n_vis = n_vis < 0 ? 0 : (n_vis > S ? S : n_vis);
+    few_keys_select(acc[c] * scale, lane, b, q, Q, S, q < Q, visible, top_k, temperature, indices_out, gates_out, scores_out);
+  }
+}
+
+// The same for very many queries (all tokens of a layer at once): a lane scores a block of 4 queries x 4 keys,
+// so that every value read from shared memory feeds four multiply-adds instead of one and the arithmetic,
+// not the shared-memory pipe, sets the time.  A warp owns 32 queries (lane (qg, kg): queries qg + 8 i, keys
+// 4 kg + j) and walks the features in tiles of 64 that it stages itself, the next tile's loads in flight
+// while it computes; each score is still the strictly sequential fused multiply-add over d.
+constexpr int kBlkWarps = 8;
+constexpr int kBlkQueries = 32;                              // per warp
+constexpr int kBlkTile = 64;                                 // features per staged tile
+constexpr int kBlkRow4 = kBlkTile / 4 + 1;                   // float4 per staged query row: 8 consecutive rows hit all banks
+
+__host__ __device__ constexpr size_t blocked_smem_bytes(int D) {
+  return sizeof(float4) * ((size_t)(D / 4) * kFewKeys + (size_t)kBlkWarps * kBlkQueries * kBlkRow4);
+}
+
+template <typename TQ>
+__global__ void __launch_bounds__(kBlkWarps * 32, 2)
+topk_route_blocked_kernel(const TQ* __restrict__ queries, const float* __restrict__ keys,
+                          const int32_t* __restrict__ visible, int64_t Q, int S, int D, int top_k, float scale,
+                          float temperature, int64_t* __restrict__ indices_out, float* __restrict__ gates_out,
+                          float* __restrict__ scores_out) {
+  extern __shared__ float4 s_blk[];                            // keys [D/4][kFewKeys], then per warp [32][kBlkRow4]
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t b = blockIdx.y;
+  const int D4 = D >> 2;
+  float4* s_keys = s_blk;
+  float4* s_q = s_blk + (size_t)D4 * kFewKeys + (size_t)warp * kBlkQueries * kBlkRow4;
+  const int64_t first = ((int64_t)blockIdx.x * kBlkWarps + warp) * kBlkQueries;    // this warp's first query
+  const int rows_here = Q - first < kBlkQueries ? (Q - first > 0 ? (int)(Q - first) : 0) : kBlkQueries;
+
+  const float4* kb = reinterpret_cast<const float4*>(keys + b * (int64_t)S * D);
+  // key 4 kg + j sits at position 4 j + kg of its feature row: the four lanes kg that read their j-th key
+  // together read neighbouring 16-byte words
+  for (int e = threadIdx.x; e < D4 * kFewKeys; e += kBlkWarps * 32) {
+    const int pos = e & (kFewKeys - 1);
+    const int s = 4 * (pos & 3) + (pos >> 2);
+    const int d4 = e >> 4;
+    s_keys[e] = s < S ? __ldg(kb + (int64_t)s * D4 + d4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  }
+
+  // a tile of the warp's queries: 32 rows x 64 features; 16-byte pieces, a row's pieces in neighbouring lanes
+  constexpr int kPieces = sizeof(TQ) == 2 ? 8 : 16;            // per row and tile
+  constexpr int kLoads = kBlkQueries * kPieces / 32;            // per lane and tile
+  const TQ* qbase = queries + (b * Q + first) * D;
+  uint4 pre[kLoads];
+  auto fetch = [&](int tile) {
+#pragma unroll
+    for (int i = 0; i < kLoads; ++i) {
+      const int e = lane + 32 * i;
+      const int row = e / kPieces, piece = e % kPieces;
+      pre[i] = row < rows_here ? __ldg(reinterpret_cast<const uint4*>(qbase + (int64_t)row * D + tile * kBlkTile) + piece)
+                               : make_uint4(0u, 0u, 0u, 0u);
     }
-    const int R = top_k < n_vis ? top_k : n_vis;
-    const bool seen = s < n_vis;
-    const unsigned long long mine =
-        seen ? (((unsigned long long)ordered_bits(score) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)s)) : 0ull;
-    int rank = 0;
+  };
+  auto stage = [&]() {
 #pragma unroll
-    for (int j = 0; j < kFewKeys; ++j) {
-      const unsigned long long other = __shfl_sync(0xffffffffu, mine, (lane & 16) | j);
-      rank += other > mine ? 1 : 0;
-    }
-    if (R == n_vis) rank = s;                                  // every visible key is taken: identity order
-    const bool chosen = seen && rank < R;
-    // softmax over the chosen scores, inside the half-warp
-    const float x = chosen ? score / temperature : -CUDART_INF_F;
-    float mx = x;
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    // fmaxf drops NaN; put it back so a NaN score poisons the row as softmax does
-    const unsigned nan_mask = __ballot_sync(0xffffffffu, chosen && x != x) & (half ? 0xffff0000u : 0x0000ffffu);
-    const float e = chosen ? expf(x - mx) : 0.0f;
-    float sum = e;
-#pragma unroll
-    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (query_live) {
-      int64_t* idx_row = indices_out + (b * Q + q) * top_k;
-      float* gate_row = gates_out + (b * Q + q) * top_k;
-      if (chosen) {
-        idx_row[rank] = s;
-        gate_row[rank] = nan_mask != 0u ? CUDART_NAN_F : e / sum;
+    for (int i = 0; i < kLoads; ++i) {
+      const int e = lane + 32 * i;
+      const int row = e / kPieces, piece = e % kPieces;
+      if constexpr (sizeof(TQ) == 2) {
+        float4* dst = s_q + row * kBlkRow4 + 2 * piece;
+        dst[0] = make_float4(__uint_as_float(pre[i].x << 16), __uint_as_float(pre[i].x & 0xffff0000u),
+                             __uint_as_float(pre[i].y << 16), __uint_as_float(pre[i].y & 0xffff0000u));
+        dst[1] = make_float4(__uint_as_float(pre[i].z << 16), __uint_as_float(pre[i].z & 0xffff0000u),
+                             __uint_as_float(pre[i].w << 16), __uint_as_float(pre[i].w & 0xffff0000u));
+      } else {
+        s_q[row * kBlkRow4 + piece] = make_float4(__uint_as_float(pre[i].x), __uint_as_float(pre[i].y),
+                                                  __uint_as_float(pre[i].z), __uint_as_float(pre[i].w));
       }
-      for (int r = R + s; r < top_k; r += kFewKeys) {          // slots without a route
-        idx_row[r] = -1;
-        gate_row[r] = 0.0f;
+    }
+  };
+
+  const int kg = lane & 3, qg = lane >> 2;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  }
+  const int n_tiles = D / kBlkTile;
+  fetch(0);
+  __syncthreads();                                            // the keys are staged
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    __syncwarp();                                             // everybody is done with the tile before
+    stage();
+    if (tile + 1 < n_tiles) fetch(tile + 1);
+    __syncwarp();
+    const float4* ks = s_keys + (size_t)tile * (kBlkTile / 4) * kFewKeys + kg;
+    const float4* qs = s_q + qg * kBlkRow4;
+#pragma unroll 4
+    for (int d4 = 0; d4 < kBlkTile / 4; ++d4) {
+      float4 k4[4], q4[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) k4[j] = ks[d4 * kFewKeys + 4 * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) q4[i] = qs[8 * i * kBlkRow4 + d4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(q4[i].x, k4[j].x, acc[i][j]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(q4[i].y, k4[j].y, acc[i][j]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(q4[i].z, k4[j].z, acc[i][j]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(q4[i].w, k4[j].w, acc[i][j]);
       }
     }
+  }
+  // the scores of a query lie in four lanes: through the warp's staging area into the layout of the selection
+  // (lane (half, s): key s of the query of that half-warp)
+  __syncwarp();
+  float* sc = reinterpret_cast<float*>(s_q);                   // [32 queries][17]
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sc[(qg + 8 * i) * (kFewKeys + 1) + 4 * kg + j] = acc[i][j] * scale;
+  }
+  __syncwarp();
+  const int half = lane >> 4, s = lane & (kFewKeys - 1);
+  for (int pair = 0; pair < kBlkQueries / 2; ++pair) {
+    const int slot = 2 * pair + half;
+    const int64_t q = first + slot;
+    few_keys_select(sc[slot * (kFewKeys + 1) + s], lane, b, q, Q, S, q < Q, visible, top_k, temperature, indices_out,
+                    gates_out, scores_out);
   }
 }
 
@@ -370,6 +515,40 @@ int launch_few_keys(const TQ* queries, const float* keys, const int32_t* visible
       gates_out, scores_out);
   return check_launch("topk_route_few_keys");
 }
+
+template <typename TQ>
+int launch_blocked(const TQ* queries, const float* keys, const int32_t* visible, int64_t B, int64_t Q, int64_t S,
+                   int64_t D, int top_k, float scale, float temperature, int64_t* indices_out, float* gates_out,
+                   float* scores_out, cudaStream_t stream) {
+  const size_t need = blocked_smem_bytes(static_cast<int>(D));
+  {
+    static std::mutex mutex;
+    static size_t configured[64] = {0};
+    int device = 0;
+    cudaGetDevice(&device);
+    std::lock_guard<std::mutex> lock(mutex);
+    if (device < 0 || device >= 64 || need > configured[device]) {
+      const cudaError_t opted = cudaFuncSetAttribute(topk_route_blocked_kernel<TQ>,
+                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(need));
+      GRMX_REQUIRE(opted == cudaSuccess, "grmx_topk_route: shared-memory opt-in failed: %s", cudaGetErrorString(opted));
+      if (device >= 0 && device < 64) configured[device] = need;
+    }
+  }
+  constexpr int per_cta = kBlkWarps * kBlkQueries;
+  const dim3 grid(static_cast<unsigned>((Q + per_cta - 1) / per_cta), static_cast<unsigned>(B));
+  topk_route_blocked_kernel<TQ><<<grid, kBlkWarps * 32, need, stream>>>(queries, keys, visible, Q, static_cast<int>(S),
+                                                                        static_cast<int>(D), top_k, scale, temperature,
+                                                                        indices_out, gates_out, scores_out);
+  return check_launch("topk_route_blocked");
+}
+// GRMX_ROUTE_BLOCKED=off keeps very many queries on the lane-per-key kernel
+bool blocked_form_applies(int64_t B, int64_t Q, int64_t D) {
+  static const bool disabled = [] {
+    const char* env = getenv("GRMX_ROUTE_BLOCKED");
+    return env != nullptr && strcmp(env, "off") == 0;
+  }();
+  return !disabled && B * Q >= kFewManyQueries && D % kBlkTile == 0;
+}
 }  // namespace
 }  // namespace grmx
 
@@ -393,6 +572,10 @@ extern "C" int grmx_topk_route(const float* queries, const float* keys, const in
     // measured at 8 x 512 queries of 512 features: one query per half-warp and 16 warps per CTA
     // (15.9 us against 29 us with four queries per half-warp and 4 warps, 43 us for the kernel below)
     // many CTAs per SM: two queries per half-warp share each key load (116 against 125 us at 65536 queries)
+    if (blocked_form_applies(B, Q, D)) {
+      return launch_blocked<float>(queries, keys, visible, B, Q, S, D, top_k, scale, temperature, indices_out, gates_out,
+                                   scores_out, static_cast<cudaStream_t>(stream));
+    }
     if (B * Q >= kFewManyQueries) {
       return launch_few_keys<2, 8, float>(queries, keys, visible, B, Q, S, D, top_k, scale, temperature, indices_out,
                                           gates_out, scores_out, static_cast<cudaStream_t>(stream));
@@ -422,6 +605,11 @@ extern "C" int grmx_topk_route_bf16q(const void* queries_bf16, const float* keys
     return fail(GRMX_ERR_UNSUPPORTED,
                 "%s: covers 1..%d keys, at least 64 queries per batch row, D %% 8 == 0, D <= %d, 16-byte aligned "
                 "inputs; widen the queries to float32 and call grmx_topk_route otherwise", who, kFewKeys, kFewMaxD);
+  }
+  if (blocked_form_applies(B, Q, D)) {
+    return launch_blocked<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(queries_bf16), keys, visible, B, Q, S, D, top_k,
+                                         scale, temperature, indices_out, gates_out, scores_out,
+                                         static_cast<cudaStream_t>(stream));
   }
   if (B * Q >= kFewManyQueries) {
     return launch_few_keys<2, 8, __nv_bfloat16>(static_cast<const __nv_bfloat16*>(queries_bf16), keys, visible, B, Q, S,
