@@ -248,6 +248,58 @@ __device__ __forceinline__ void rows_apply(const float4 (&m)[8], const float* q_
   }
 }
 
+// The same for K a multiple of 64, with four times fewer shared-memory reads per multiply-add: lane
+// (kq, rg) = (lane / 8, lane % 8) holds rows 4 rg .. 4 rg + 3 of the unit over a quarter of a span of columns
+// (128 columns when K is a multiple of 128, else 64), 16 columns (four 16-byte pieces) at a time, so a query
+// value read from shared memory feeds four rows.  The pieces of a lane's columns are visited in an order
+// rotated by rg (eight lanes that read together hit eight different bank groups, four with the narrow span;
+// the query is read in the same order).  The partial sums of the four lanes kq of a row group are added by
+// shuffles and lane kq adds row 4 rg + kq to the sums.
+template <int K, int NB, int PIECES>
+__device__ __forceinline__ void rows_apply_tiled(const float4 (&m)[4][4], const float* q_cols, int first_piece, int rg, int kq,
+                                                 const int* list_q, const float* list_g, int i0, int left, float* acc_rows,
+                                                 int Hp, bool row_live) {
+  float dot[4][NB];
+  const float4* qv[NB];
+#pragma unroll
+  for (int u = 0; u < NB; ++u) {
+    qv[u] = reinterpret_cast<const float4*>(q_cols + list_q[u < left ? i0 + u : i0] * K);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dot[i][u] = 0.0f;
+  }
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int piece = (first_piece + p + rg) & (PIECES - 1);
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      const float4 x = qv[u][piece];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        dot[i][u] = fmaf(m[i][p].x, x.x, dot[i][u]);
+        dot[i][u] = fmaf(m[i][p].y, x.y, dot[i][u]);
+        dot[i][u] = fmaf(m[i][p].z, x.z, dot[i][u]);
+        dot[i][u] = fmaf(m[i][p].w, x.w, dot[i][u]);
+      }
+    }
+  }
+  // lanes kq = 0..3 of a row group differ in lane bits 3 and 4
+#pragma unroll
+  for (int u = 0; u < NB; ++u) {
+    float mine = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float t = dot[i][u];
+      t += __shfl_xor_sync(0xffffffffu, t, 8);
+      t += __shfl_xor_sync(0xffffffffu, t, 16);
+      if (i == kq) mine = t;
+    }
+    if (u < left && row_live) {
+      float* a = acc_rows + list_q[i0 + u] * Hp;
+      *a = fmaf(list_g[i0 + u], mine, *a);
+    }
+  }
+}
+
 template <int KC>                      // 32-float chunks per matrix row: K = 32 * KC
 __global__ void __launch_bounds__(kRowsThreads)
 retrieve_fuse_rows_kernel(const float* __restrict__ archive, const int64_t* __restrict__ indices,
@@ -407,6 +459,47 @@ retrieve_fuse_rows_kernel(const float* __restrict__ archive, const int64_t* __re
       if (!mbar_wait(&bar_full[stage], static_cast<uint32_t>(v / per_warp) & 1u, s_abort)) break;
       const int slot = s_chosen[ci];
       const int begin = s_start[slot], end = s_start[slot + 1];
+      if constexpr (K % 64 == 0) {
+        // ---- four rows x a quarter span per lane (see rows_apply_tiled) ----
+        constexpr int kSpan = K % 128 == 0 ? 128 : 64;          // columns per span
+        constexpr int kPieces = kSpan / 16;                     // 16-byte pieces of a lane's quarter: 8 or 4
+        const int rg = lane & 7, kq = lane >> 3;
+        const int rows_here = min(32, H - 32 * rb);
+        const float* unit = s_ring + stage * kUnitFloats;
+        const bool row_live = 4 * rg + kq < rows_here;          // the row this lane adds to the sums
+        float* acc_rows = s_acc + set * Q * Hp + 32 * rb + 4 * rg + kq;
+#pragma unroll 1
+        for (int span = 0; span < K / kSpan; ++span) {
+#pragma unroll 1
+          for (int half = 0; half < kPieces / 4; ++half) {
+            float4 m[4][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int r = min(4 * rg + i, rows_here - 1);     // rows past the end are computed and dropped
+              const float4* row = reinterpret_cast<const float4*>(unit + r * K + kSpan * span + (kSpan / 4) * kq);
+#pragma unroll
+              for (int p4 = 0; p4 < 4; ++p4) m[i][p4] = row[(4 * half + p4 + rg) & (kPieces - 1)];
+            }
+            if (span == K / kSpan - 1 && half == kPieces / 4 - 1) {   // the unit is in registers: its stage can be refilled
+              __syncwarp();
+              if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_empty[stage])) : "memory");
+              }
+            }
+            const float* q_cols = s_q + kSpan * span + (kSpan / 4) * kq;
+            for (int i0 = begin; i0 < end;) {
+              const int left = end - i0;                        // uniform across the warp
+              if (left > 4) {
+                rows_apply_tiled<K, kRowsBatch, kPieces>(m, q_cols, 4 * half, rg, kq, s_list_q, s_list_g, i0, left, acc_rows, Hp, row_live);
+                i0 += kRowsBatch;
+              } else {
+                rows_apply_tiled<K, 4, kPieces>(m, q_cols, 4 * half, rg, kq, s_list_q, s_list_g, i0, left, acc_rows, Hp, row_live);
+                i0 += 4;
+              }
+            }
+          }
+        }
+      } else {
       const float4* row = reinterpret_cast<const float4*>(s_ring + stage * kUnitFloats + lane_read * K);
 #pragma unroll 1
       for (int c = 0; c < KC; ++c) {
@@ -432,6 +525,7 @@ retrieve_fuse_rows_kernel(const float* __restrict__ archive, const int64_t* __re
             i0 += 4;
           }
         }
+      }
       }
     }
   }
