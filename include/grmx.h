@@ -367,6 +367,19 @@ int grmx_select_fuse(const void* states, const int64_t* indices, const float* ga
                      int64_t Q, int64_t S, int64_t R, int64_t H, int dtype, int mode, void* stream);
 
 /*
+ * out = LayerNorm(a + b) * ln_weight + ln_bias over rows of H values (dtype GRMX_F32 or GRMX_BF16 for a, b and
+ * out; sum, mean and variance in fp32; ln_weight / ln_bias fp32 or NULL), one pass, both rows requested at
+ * once.  The same arithmetic as grmx_select_fuse in GRMX_FUSE_RESIDUAL_LN mode with b as the only candidate
+ * and a unit gate.  Rows of whole 16-byte pieces, 16-byte aligned tensors, H <= 1024; GRMX_ERR_UNSUPPORTED
+ * otherwise.
+ *
+ * Replaces the residual block between the layers of the stack, self.layer_norm(outputs + x)
+ * (grm/core/multilayer_grm.py:93,96), which the reference runs as an add followed by nn.LayerNorm.
+ */
+int grmx_add_layer_norm(const void* a, const void* b, const float* ln_weight, const float* ln_bias,
+                        float ln_eps, void* out, int64_t rows, int64_t H, int dtype, void* stream);
+
+/*
  * out[n,:] = x[n,:] / max(||x[n,:]||_2, eps) for N rows of K elements, in one pass (fp32 sum of squares).
  * (in_dtype, out_dtype) is (F32,F32), (BF16,BF16) or (F32,BF16): the last also rounds to the type the
  * tensor-core scan reads.  Rows must be whole 16-byte pieces (K % 4 == 0 for fp32, K % 8 == 0 for bf16),

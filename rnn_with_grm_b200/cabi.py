@@ -87,6 +87,10 @@ SIGNATURES = {
         c_int,
         [c_void_p] * 7 + [c_float, c_void_p] + [c_int64] * 6 + [c_int, c_void_p],
     ),
+    "grmx_add_layer_norm": (
+        c_int,
+        [c_void_p] * 4 + [c_float, c_void_p, c_int64, c_int64, c_int, c_void_p],
+    ),
     "grmx_select_fuse": (
         c_int,
         [c_void_p] * 6 + [c_float, c_void_p] + [c_int64] * 5 + [c_int, c_int, c_void_p],

@@ -269,6 +269,97 @@ void launch_select_fuse(const void* states, const int64_t* indices, const float*
 #undef GRMX_SELECT
 }
 
+
+// LayerNorm(a + b) over rows of H values, one pass, a warp per row: the residual block between layers
+// (grm/core/multilayer_grm.py:93,96).  The same arithmetic as the residual rule above with b as the only
+// candidate and a unit gate (sum in fp32, one rounding; mean and variance in the same order), without the
+// route bookkeeping and its dependent loads: both rows are requested at once.
+template <typename T, int VEC, int kPieces>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+add_layer_norm_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ ln_weight,
+                      const float* __restrict__ ln_bias, float ln_eps, T* __restrict__ out, int64_t rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;   // whole warps leave together; no CTA barrier below
+  uint4 ra[kPieces], rb[kPieces];
+#pragma unroll
+  for (int i = 0; i < kPieces; ++i) {
+    const int h = (lane + 32 * i) * VEC;
+    ra[i] = h < H ? load_raw16(a + row * H + h) : make_uint4(0u, 0u, 0u, 0u);
+    rb[i] = h < H ? load_raw16(b + row * H + h) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float x[kPieces][VEC];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kPieces; ++i) {
+    float other[VEC];
+    unpack_piece<T, VEC>(ra[i], x[i]);
+    unpack_piece<T, VEC>(rb[i], other);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      x[i][j] += other[j];
+      sum += x[i][j];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float mean = sum / (float)H;
+  float sq = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kPieces; ++i) {
+    const int h = (lane + 32 * i) * VEC;
+    if (h < H) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float d = x[i][j] - mean;
+        sq = fmaf(d, d, sq);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  const float rstd = rsqrtf(sq / (float)H + ln_eps);
+#pragma unroll
+  for (int i = 0; i < kPieces; ++i) {
+    const int h = (lane + 32 * i) * VEC;
+    if (h < H) {
+      float y[VEC];
+#pragma unroll
+      for (int j4 = 0; j4 < VEC / 4; ++j4) {
+        const float4 w4 = ln_weight != nullptr ? __ldg(reinterpret_cast<const float4*>(ln_weight + h) + j4)
+                                               : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        const float4 b4 = ln_bias != nullptr ? __ldg(reinterpret_cast<const float4*>(ln_bias + h) + j4)
+                                             : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+        const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float v = (x[i][4 * j4 + j] - mean) * rstd;
+          if (ln_weight != nullptr) v *= wv[j];
+          if (ln_bias != nullptr) v += bv[j];
+          y[4 * j4 + j] = v;
+        }
+      }
+      store_piece<T, VEC>(out + row * H + h, y);
+    }
+  }
+}
+
+template <typename T, int VEC>
+void launch_add_layer_norm(const void* a, const void* b, const float* w, const float* bias, float eps, void* out,
+                           int64_t rows, int H, cudaStream_t s) {
+  const unsigned blocks = static_cast<unsigned>((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+  const int needed = (H + 32 * VEC - 1) / (32 * VEC);
+#define GRMX_ALN(P)                                                                                                  \
+  add_layer_norm_kernel<T, VEC, P><<<blocks, kWarpsPerCta * 32, 0, s>>>(static_cast<const T*>(a), static_cast<const T*>(b), \
+                                                                          w, bias, eps, static_cast<T*>(out), rows, H)
+  if (needed <= 1) GRMX_ALN(1);
+  else if (needed <= 2) GRMX_ALN(2);
+  else if (needed <= 4) GRMX_ALN(4);
+  else GRMX_ALN(kMaxPerLane / VEC);
+#undef GRMX_ALN
+}
+
 }  // namespace
 }  // namespace grmx
 
@@ -308,4 +399,26 @@ extern "C" int grmx_select_fuse(const void* states, const int64_t* indices, cons
     else launch_select_fuse<__nv_bfloat16, 1>(states, indices, gates, online, ln_weight, ln_bias, ln_eps, out, BQ, (int)S, (int)R, (int)H, mode, s, err);
   }
   return check_launch("select_fuse");
+}
+
+extern "C" int grmx_add_layer_norm(const void* a, const void* b, const float* ln_weight, const float* ln_bias,
+                                   float ln_eps, void* out, int64_t rows, int64_t H, int dtype, void* stream) {
+  using namespace grmx;
+  const char* who = "grmx_add_layer_norm";
+  GRMX_REQUIRE(rows >= 0 && H >= 0, "%s: negative size", who);
+  GRMX_REQUIRE(dtype == GRMX_F32 || dtype == GRMX_BF16, "%s: dtype must be f32 or bf16", who);
+  if (rows * H == 0) return GRMX_OK;
+  GRMX_REQUIRE(a != nullptr && b != nullptr && out != nullptr, "%s: NULL tensor", who);
+  const int per16 = dtype == GRMX_F32 ? 4 : 8;
+  const uintptr_t bases = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out) |
+                          reinterpret_cast<uintptr_t>(ln_weight) | reinterpret_cast<uintptr_t>(ln_bias);
+  if (H % per16 != 0 || (bases & 15u) != 0 || H > 32 * kMaxPerLane) {
+    return fail(GRMX_ERR_UNSUPPORTED, "%s: needs rows of whole 16-byte pieces, 16-byte aligned tensors and H <= %d", who,
+                32 * kMaxPerLane);
+  }
+  GRMX_REQUIRE((rows + kWarpsPerCta - 1) / kWarpsPerCta <= 0x7fffffffLL, "%s: grid too large", who);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == GRMX_F32) launch_add_layer_norm<float, 4>(a, b, ln_weight, ln_bias, ln_eps, out, rows, (int)H, s);
+  else launch_add_layer_norm<__nv_bfloat16, 8>(a, b, ln_weight, ln_bias, ln_eps, out, rows, (int)H, s);
+  return check_launch("add_layer_norm");
 }

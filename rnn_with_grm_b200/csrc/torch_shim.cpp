@@ -341,6 +341,34 @@ at::Tensor select_fuse_cuda(const at::Tensor& states, const at::Tensor& indices,
   return out;
 }
 
+// LayerNorm(a + b) over the last dimension (fp32 or bf16 rows of whole 16-byte pieces, H <= 1024)
+at::Tensor add_layer_norm_cuda(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& ln_weight,
+                               const c10::optional<at::Tensor>& ln_bias, double ln_eps) {
+  TORCH_CHECK(a.sizes() == b.sizes() && a.dim() >= 1, "a and b must have the same shape");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type() && (a.scalar_type() == at::kFloat || a.scalar_type() == at::kBFloat16),
+              "a and b must both be float32 or bfloat16");
+  require_cuda(a, "a");
+  require_cuda(b, "b");
+  c10::cuda::CUDAGuard guard(a.device());
+  auto ca = a.contiguous(), cb = b.contiguous();
+  const int64_t H = ca.size(-1);
+  const int64_t rows = H > 0 ? ca.numel() / H : 0;
+  at::Tensor w_keep, b_keep;
+  auto opt = [&](const c10::optional<at::Tensor>& t, const char* name, at::Tensor& keep) -> const float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    require_cuda(*t, name);
+    keep = t->to(at::kFloat).contiguous();
+    TORCH_CHECK(keep.numel() == H, name, " has the wrong shape");
+    return keep.data_ptr<float>();
+  };
+  const float* w_ptr = opt(ln_weight, "ln_weight", w_keep);
+  const float* b_ptr = opt(ln_bias, "ln_bias", b_keep);
+  at::Tensor out = at::empty_like(ca);
+  check_status(grmx_add_layer_norm(ca.data_ptr(), cb.data_ptr(), w_ptr, b_ptr, static_cast<float>(ln_eps), out.data_ptr(),
+                                   rows, H, ca.scalar_type() == at::kFloat ? GRMX_F32 : GRMX_BF16, current_stream()));
+  return out;
+}
+
 std::tuple<at::Tensor, at::Tensor> chunk_scan_segments_cuda(const at::Tensor& keys, const at::Tensor& values,
                                                             const at::Tensor& queries, const at::Tensor& memory,
                                                             double memory_decay, at::Tensor archive, int64_t first_slot,
@@ -548,6 +576,7 @@ TORCH_LIBRARY(grmx, m) {
   m.def("l2_normalize(Tensor x, float eps, bool to_bfloat16) -> Tensor");
   m.def("project_normalize(Tensor x, Tensor weights, Tensor? bias, float eps) -> (Tensor a, Tensor b)");
   m.def("archive_push(Tensor memory, Tensor(a!) archive, Tensor(b!)? shadow, int slot) -> ()");
+  m.def("add_layer_norm(Tensor a, Tensor b, Tensor? ln_weight, Tensor? ln_bias, float ln_eps) -> Tensor");
   m.def("select_fuse(Tensor states, Tensor indices, Tensor gates, Tensor? online, Tensor? ln_weight, Tensor? ln_bias, float ln_eps, int mode) -> Tensor");
 }
 
@@ -558,6 +587,7 @@ TORCH_LIBRARY_IMPL(grmx, CUDA, m) {
   m.impl("retrieve_fuse", retrieve_fuse_cuda);
   m.impl("retrieve_fuse_tc", retrieve_fuse_tc_cuda);
   m.impl("select_fuse", select_fuse_cuda);
+  m.impl("add_layer_norm", add_layer_norm_cuda);
   m.impl("archive_push", archive_push_cuda);
   m.impl("project_normalize", project_normalize_cuda);
   m.impl("l2_normalize", l2_normalize_cuda);

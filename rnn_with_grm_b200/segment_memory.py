@@ -707,23 +707,16 @@ class StackedSegmentMemoryRunner:
         # False: stop after the stack's own output projection (the 512 -> vocabulary layer of the language-model
         # wrapper is not part of the memory path; timing with and without it separates the two)
         self.vocabulary_projection = True
-        self._unit_routes: Dict[Tuple[int, str], Tuple[Tensor, Tensor]] = {}
         self._fp32_cache: Dict[int, Tuple[Tensor, Tensor, int]] = {}
 
     def _add_layer_norm(self, out: Tensor, h: Tensor, weight: Optional[Tensor], bias: Optional[Tensor]) -> Tensor:
-        """``LayerNorm(out + h)`` in one pass: the residual rule of the fusion kernel with ``out`` as the
-        only candidate state and a unit gate (sum and normalisation in fp32, no rounded intermediate)."""
+        """``LayerNorm(out + h)`` in one pass (``torch.ops.grmx.add_layer_norm``: sum and normalisation in fp32,
+        no rounded intermediate; multilayer_grm.py:93,96)."""
         H = h.shape[-1]
+        per16 = 4 if h.dtype == torch.float32 else 8
         if not (h.is_cuda and h.dtype == out.dtype and h.dtype in (torch.float32, torch.bfloat16) and H <= 1024
-                and weight is not None and bias is not None):
+                and H % per16 == 0 and weight is not None and bias is not None):
             return F.layer_norm(out + h, (H,), weight, bias, 1e-5)
-        tokens = h.numel() // H
-        key = (tokens, str(h.device))
-        unit = self._unit_routes.get(key)
-        if unit is None:
-            unit = (torch.zeros(1, tokens, 1, device=h.device, dtype=torch.int64),
-                    torch.ones(1, tokens, 1, device=h.device, dtype=torch.float32))
-            self._unit_routes[key] = unit
         params = []
         for t in (weight, bias):
             cached = self._fp32_cache.get(id(t))
@@ -731,9 +724,7 @@ class StackedSegmentMemoryRunner:
                 cached = (t, t.float(), t._version)
                 self._fp32_cache[id(t)] = cached
             params.append(cached[1])
-        fused = torch.ops.grmx.select_fuse(out.reshape(1, tokens, 1, H), unit[0], unit[1], h.reshape(1, tokens, H),
-                                           params[0], params[1], 1e-5, FUSE_RESIDUAL_LN)
-        return fused.view(h.shape)
+        return torch.ops.grmx.add_layer_norm(h, out, params[0], params[1], 1e-5)
 
     @torch.no_grad()
     def forward(self, x: Tensor, reset_memory: bool = True):

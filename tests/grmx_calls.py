@@ -170,6 +170,16 @@ def retrieve_fuse_tc(archive, indices, gates, queries, online=None, ln_weight=No
     return out
 
 
+def add_layer_norm(a, b, ln_weight=None, ln_bias=None, eps=1e-5):
+    lib = cabi.load()
+    H = a.shape[-1]
+    out = torch.empty_like(a)
+    dtype = cabi.F32 if a.dtype == torch.float32 else cabi.BF16
+    cabi.check(lib.grmx_add_layer_norm(cabi.ptr(a), cabi.ptr(b), cabi.ptr(ln_weight), cabi.ptr(ln_bias), float(eps),
+                                       cabi.ptr(out), a.numel() // H, H, dtype, cabi.current_stream()))
+    return out
+
+
 def select_fuse(states, indices, gates, online=None, ln_weight=None, ln_bias=None, eps=1e-5,
                 mode=cabi.FUSE_RESIDUAL_LN):
     lib = cabi.load()

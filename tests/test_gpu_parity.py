@@ -513,6 +513,33 @@ def test_select_fuse_equals_the_fused_chain_on_dense_candidates(dtype, tol, H):
     assert cabi.device_error_word() == 0
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_TOL), (torch.bfloat16, LOWP_TOL)])
+@pytest.mark.parametrize("rows,H", [(5, 64), (4099, 512), (33, 1000), (7, 1024), (3, 8)])
+def test_add_layer_norm_is_the_residual_rule_with_one_candidate(dtype, tol, rows, H):
+    """LayerNorm(a + b) in one pass: against float64 on the values the kernel sees, and bit for bit the same as
+    the fusion kernel's residual rule with b as the only candidate and a unit gate."""
+    rng = np.random.default_rng(rows + H)
+    a, b = (dev(rng.standard_normal((rows, H)).astype(np.float32), dtype) for _ in range(2))
+    w = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    bias = (0.1 * rng.standard_normal(H)).astype(np.float32)
+    got = gx.add_layer_norm(a, b, dev(w), dev(bias))
+    x = host(a).astype(np.float64) + host(b).astype(np.float64)
+    want = (x - x.mean(-1, keepdims=True)) / np.sqrt(x.var(-1, keepdims=True) + 1e-5) * w + bias
+    close(got, want, tol)
+    unit_idx = torch.zeros(1, rows, 1, device=DEV, dtype=torch.int64)
+    unit_gate = torch.ones(1, rows, 1, device=DEV)
+    same = gx.select_fuse(b.view(1, rows, 1, H), unit_idx, unit_gate, a.view(1, rows, H), dev(w), dev(bias), 1e-5,
+                          cabi.FUSE_RESIDUAL_LN)
+    assert torch.equal(got, same.view(rows, H))
+    plain = gx.add_layer_norm(a, b)                          # no affine part
+    close(plain, (x - x.mean(-1, keepdims=True)) / np.sqrt(x.var(-1, keepdims=True) + 1e-5), tol)
+    lib = cabi.load()
+    odd = torch.zeros(2, 6, device=DEV, dtype=dtype)        # rows that are not whole 16-byte pieces
+    rc = lib.grmx_add_layer_norm(cabi.ptr(odd), cabi.ptr(odd), None, None, 1e-5, cabi.ptr(odd), 2, 6,
+                                 cabi.F32 if dtype == torch.float32 else cabi.BF16, cabi.current_stream())
+    assert rc == 2 and b"16-byte" in lib.grmx_last_error()
+
+
 # --------------------------------------------------------------------------- chunk scan, tcgen05 path
 
 @pytest.mark.parametrize("B,S,Q,R,H,seg,mode", [(1, 3, 128, 2, 64, None, cabi.FUSE_RESIDUAL_LN),
