@@ -308,6 +308,10 @@ retrieve_fuse_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         continue;
       }
+      // the row of the online state is needed when the products of the tile are done: ask L2 for it now
+      if (p.mode == GRMX_FUSE_RESIDUAL_LN && h_row != nullptr) {
+        for (int j = 0; j < H / 64; ++j) asm volatile("prefetch.global.L2 [%0];" ::"l"(h_row + 8 * j));
+      }
       GRMX_WAIT(bar_acc_ready, na)
       tc_fence_after();
       if (p.mode == GRMX_FUSE_CONTRIB) {
@@ -328,16 +332,29 @@ retrieve_fuse_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
         }
       } else {
-        // pass 1: x = contribution + online state, written back over the accumulator; row sum
-        float sum = 0.0f;
+        // pass 1: x = contribution + online state, written back over the accumulator; row sum and sum of
+        // squares (one pass over TMEM less than a variance about the mean: with rows of at most 512 values
+        // of order one the difference of the two means is good to a few parts in a million, far inside the
+        // bf16 rounding of the output)
+        float sum = 0.0f, sq = 0.0f;
+        // the 64 bytes of online state that go with 32 columns are loaded one step ahead
+        uint4 ahead[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ahead[j] = h_row != nullptr ? __ldg(h_row + j) : make_uint4(0u, 0u, 0u, 0u);
         for (int c0 = 0; c0 < H; c0 += 32) {
           uint32_t v[32];
           tc_ld32_async(lane_addr + c0, v);
+          uint4 now[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) now[j] = ahead[j];
+          if (c0 + 32 < H && h_row != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ahead[j] = __ldg(h_row + (c0 + 32) / 8 + j);
+          }
           tc_wait_ld();
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            uint4 hw = make_uint4(0u, 0u, 0u, 0u);
-            if (h_row != nullptr) hw = __ldg(h_row + c0 / 8 + j);
+            const uint4 hw = now[j];
             const uint32_t words[4] = {hw.x, hw.y, hw.z, hw.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -347,26 +364,15 @@ retrieve_fuse_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
               v[8 * j + 2 * i] = __float_as_uint(x0);
               v[8 * j + 2 * i + 1] = __float_as_uint(x1);
               sum += x0 + x1;
+              sq = fmaf(x0, x0, fmaf(x1, x1, sq));
             }
           }
           tc_st32_async(lane_addr + c0, v);
         }
         tc_wait_st();
         const float mean = sum * inv_h;
-        // pass 2: variance about the mean
-        float sq = 0.0f;
-        for (int c0 = 0; c0 < H; c0 += 32) {
-          uint32_t v[32];
-          tc_ld32_async(lane_addr + c0, v);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float d = __uint_as_float(v[j]) - mean;
-            sq = fmaf(d, d, sq);
-          }
-        }
-        const float rstd = rsqrtf(sq * inv_h + p.eps);
-        // pass 3: normalise (a token without a live route keeps its online state as it is) and store
+        const float rstd = rsqrtf(fmaxf(sq * inv_h - mean * mean, 0.0f) + p.eps);
+        // pass 2: normalise (a token without a live route keeps its online state as it is) and store
         for (int c0 = 0; c0 < H; c0 += 32) {
           uint32_t v[32];
           tc_ld32_async(lane_addr + c0, v);
