@@ -594,6 +594,59 @@ def full_occupancy_scan(lib, device, hbm_peak, launches=5):
             "bytes": nbytes, "row_tokens_per_s": rows * T / (ms * 1e-3)}
 
 
+def config2_batches_in_flight(lib, device, hbm_peak, batches=64):
+    """The kernel-alone configuration with TWO independent batches in flight: two streams, each replaying its own
+    graph of `batches` launches over its own rotating inputs.  The headline times batches one after the other,
+    where a launch of 128 CTAs leaves 20 SMs idle and pays its prologue and drain every 24 us; here the second
+    stream fills both.  Context for the headline's roofline fraction, not a replacement for it."""
+    from rnn_with_grm_b200 import cabi
+
+    rows, T, K, V, decay = CFG2["B"] * CFG2["Hd"], CFG2["T"], CFG2["K"], CFG2["V"], CFG2["decay"]
+    set_bytes = rows * T * (2 * K + 2 * V) * 2
+    n_sets = max(2, math.ceil(1.2 * L2_BYTES / set_bytes))
+    lanes, keep = [], []                                     # the graphs hold raw pointers: the tensors must outlive them
+    for lane in range(2):
+        sets = []
+        for s_ in range(n_sets):
+            k, v, q = make_scan_inputs(rows, T, K, V, device, seed=5000 + 100 * lane + s_)
+            sets.append((k, v, q, torch.empty(rows, T, V, device=device, dtype=torch.bfloat16)))
+        m_in = torch.zeros(rows, V, K, device=device)
+        m_out = torch.empty_like(m_in)
+
+        def batch(i, stream, sets=sets, m_in=m_in, m_out=m_out):
+            k, v, q, o = sets[i % n_sets]
+            cabi.check(lib.grmx_chunk_scan_fwd(k.data_ptr(), v.data_ptr(), q.data_ptr(), m_in.data_ptr(), o.data_ptr(),
+                                               m_out.data_ptr(), rows, T, K, V, decay, cabi.BF16, cabi.F32,
+                                               cabi.PATH_AUTO, stream))
+
+        keep.append((sets, m_in, m_out))
+        lanes.append(GraphedStep(batch, batches, eager_warmup=2))
+    replays = 8
+    for step in lanes:
+        with torch.cuda.stream(step.stream):
+            step.graph.replay()
+    torch.cuda.synchronize()
+    start = torch.cuda.Event(enable_timing=True)
+    ends = [torch.cuda.Event(enable_timing=True) for _ in lanes]
+    start.record(torch.cuda.current_stream())
+    for step in lanes:
+        step.stream.wait_event(start)
+    for _ in range(replays):
+        for step in lanes:
+            with torch.cuda.stream(step.stream):
+                step.graph.replay()
+    for step, end in zip(lanes, ends):
+        end.record(step.stream)
+    torch.cuda.synchronize()
+    ms = max(start.elapsed_time(end) for end in ends)
+    n = 2 * batches * replays
+    nbytes = rows * T * (2 * (2 * K + V) + 2 * V)
+    del keep
+    return {"batches_in_flight": 2, "us_per_batch": ms * 1e3 / n, "tokens_per_s": CFG2["B"] * T * n / (ms * 1e-3),
+            "gbs": nbytes * n / ms / 1e6, "frac_hbm": nbytes * n / ms / 1e6 / hbm_peak,
+            "timing": "CUDA events on both streams, the later end counts"}
+
+
 def wide_head_scan(lib, device, hbm_peak, rows=296, T=8192, launches=3):
     """The scan at d_k = d_v = 128 (the head size of the scale-out configuration) alone: `rows` rows of T
     tokens, inputs larger than L2."""
@@ -853,6 +906,8 @@ def other_workloads(lib, device, hbm_peak):
     out["full_occupancy_scan"] = full_occupancy_scan(lib, device, hbm_peak)
     out["wide_head_scan"] = wide_head_scan(lib, device, hbm_peak)
     out["cfg2_backward"] = config2_backward(lib, device)
+    out["cfg2_two_batches_in_flight"] = config2_batches_in_flight(lib, device, hbm_peak)
+    torch.cuda.empty_cache()
     torch.cuda.empty_cache()
     out["cfg4_model"] = config4_model(device)
     out["cfg4_segment_retrieval"] = segment_retrieval(lib, device, hbm_peak)
