@@ -378,8 +378,9 @@ retrieve_fuse_rows_kernel(const float* __restrict__ archive, const int64_t* __re
     s_chosen[S] = chosen;
   }
   __syncthreads();
-  // live entries grouped by slot, in entry order within a slot (deterministic): a warp per slot, 32 entries a step
-  for (int slot = warp; slot < S; slot += kRowsThreads / 32) {
+  // live entries grouped by slot, in entry order within a slot (deterministic): a warp per slot, 32 entries a
+  // step.  Only the consumers need the lists; the producer knows the chosen slots and starts its copies.
+  for (int slot = warp; warp < kRowsConsumers && slot < S; slot += kRowsConsumers) {
     int at = s_start[slot];
     const int stop = s_start[slot + 1];
     for (int e0 = 0; e0 < entries && at < stop; e0 += 32) {
@@ -394,7 +395,7 @@ retrieve_fuse_rows_kernel(const float* __restrict__ archive, const int64_t* __re
       at += __popc(votes);
     }
   }
-  __syncthreads();
+  if (warp < kRowsConsumers) asm volatile("bar.sync 1, %0;" ::"n"(kRowsConsumers * 32) : "memory");
   const int n_chosen = s_chosen[S];
   const int per_warp = plan.n_stages / kRowsConsumers;          // stages of a consumer warp's own ring
 
