@@ -418,7 +418,8 @@ def test_retrieve_fuse_modes(H, K):
 @pytest.mark.parametrize("B,S,Q,R,H,K", [(3, 9, 5, 4, 64, 64), (2, 32, 32, 8, 128, 128), (70, 32, 32, 4, 64, 64),
                                          (2, 5, 7, 3, 20, 32), (1, 40, 3, 2, 100, 96), (2, 6, 1, 6, 33, 160),
                                          (2, 3, 40, 2, 256, 32), (3, 17, 9, 5, 1, 64), (3, 9, 20, 5, 100, 128),
-                                         (2, 4, 13, 4, 33, 128), (65, 32, 32, 8, 128, 128)])
+                                         (2, 4, 13, 4, 33, 128), (65, 32, 32, 8, 128, 128), (2, 300, 4, 8, 32, 32),
+                                         (1, 64, 64, 1, 64, 64)])
 def test_retrieve_fuse_slot_major_form(B, S, Q, R, H, K):
     """One CTA per batch row that reads every chosen matrix once: same results as the query-major kernel
     to fp32 rounding (the sum over a query's routes runs in slot order), empty routes, repeated slots and
