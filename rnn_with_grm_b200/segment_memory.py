@@ -247,6 +247,8 @@ class SegmentMemoryRunner:
         # The scores are the same sums associated differently, equal to fp32 rounding.
         # Set it before the first call (the archive keeps the keys in the form they were pushed in).
         self.fold_routing_projection = True
+        self.parallel_summaries = True     # whole-sequence form: summaries and routing keys beside the scan
+        self._side_streams: Dict[str, torch.cuda.Stream] = {}
         # Whole segments of bf16 activations that fit the archive without evicting run as one scan
         # launch plus one routing / selection pass for all tokens (see _run_whole_sequence).
         self.fuse_segments = True
@@ -330,6 +332,14 @@ class SegmentMemoryRunner:
         return t
 
     # ---- pieces of one segment -------------------------------------------------------------
+
+    def _side_stream(self, device) -> "torch.cuda.Stream":
+        key = str(device)
+        stream = self._side_streams.get(key)
+        if stream is None:
+            stream = torch.cuda.Stream(device=device)
+            self._side_streams[key] = stream
+        return stream
 
     def _route_keys(self, summaries: Tensor) -> Tensor:
         """Segment summaries ``[B, n, D]`` as the router scores them (paper_grm.py:566-570: bias-free
@@ -497,9 +507,6 @@ class SegmentMemoryRunner:
         archive.keep_bf16_copy()
         memory = c_init.float() if c_init is not None else torch.zeros(B, self.hidden, self.key_dim, device=x.device,
                                                                        dtype=torch.float32)
-        k, q = self._keys_and_queries(x)
-        v = _linear(x, self.p, "memory_cell.value_proj")
-        summaries = archive.as_stored(x.reshape(B, n_seg, L, -1).mean(dim=2, dtype=torch.float32))
         route_q_weight = self._fp32_param("gating_unit.query_projection.weight")
         self._route_key_weight = self._fp32_param("gating_unit.key_projection.weight")
         fold = self.fold_routing_projection and self.input_size <= 2 * self.route_dim
@@ -507,9 +514,23 @@ class SegmentMemoryRunner:
         if archive.count > 0 and archive.route_keys is None:       # an archive restored from a saved state
             archive.set_route_keys(self._route_keys(archive.ordered_summaries()))
         first = archive.count                                        # head == 0 here
-        if not archive.write_ahead(summaries, self._route_keys(summaries)):
-            raise RuntimeError("the archive cannot take the segments of this call without evicting")
+        # The segment summaries and their routing keys (a mean and two small GEMMs, all of them far from
+        # filling the GPU) are needed by the routing only: they run on a stream of their own beside the
+        # projections and the scan, and the routing waits for them.
+        main = torch.cuda.current_stream(x.device)
+        side = self._side_stream(x.device) if self.parallel_summaries else main
+        if side is not main:
+            side.wait_stream(main)
+        with torch.cuda.stream(side):
+            summaries = archive.as_stored(x.reshape(B, n_seg, L, -1).mean(dim=2, dtype=torch.float32))
+            new_keys = self._route_keys(summaries)
+            if not archive.write_ahead(summaries, new_keys):
+                raise RuntimeError("the archive cannot take the segments of this call without evicting")
+        k, q = self._keys_and_queries(x)
+        v = _linear(x, self.p, "memory_cell.value_proj")
         hidden, memory = torch.ops.grmx.chunk_scan_segments(k, v, q, memory, self.decay, archive.memories, first, L)
+        if side is not main:
+            main.wait_stream(side)       # summaries and new_keys stay referenced until here: their memory is not reused
         archive.note_pushed(n_seg)
         if archive.storage_dtype != torch.float32:      # the states the scan left in the ring, as the archive stores them
             archive.memories[:, first:first + n_seg] = archive.as_stored(archive.memories[:, first:first + n_seg])
