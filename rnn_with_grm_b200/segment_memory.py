@@ -514,9 +514,9 @@ class SegmentMemoryRunner:
         if archive.count > 0 and archive.route_keys is None:       # an archive restored from a saved state
             archive.set_route_keys(self._route_keys(archive.ordered_summaries()))
         first = archive.count                                        # head == 0 here
-        # The segment summaries and their routing keys (a mean and two small GEMMs, all of them far from
-        # filling the GPU) are needed by the routing only: they run on a stream of their own beside the
-        # projections and the scan, and the routing waits for them.
+        # The segment summaries, their routing keys (a mean and two small GEMMs, all of them far from filling
+        # the GPU) and the routing depend on the layer input only: they run on a stream of their own beside
+        # the projections and the scan, and the retrieval waits for them.
         main = torch.cuda.current_stream(x.device)
         side = self._side_stream(x.device) if self.parallel_summaries else main
         if side is not main:
@@ -526,21 +526,24 @@ class SegmentMemoryRunner:
             new_keys = self._route_keys(summaries)
             if not archive.write_ahead(summaries, new_keys):
                 raise RuntimeError("the archive cannot take the segments of this call without evicting")
+            # the routing itself needs the layer input and the keys only, nothing of the scan
+            held = first + n_seg
+            gates = indices = None
+            if held > 1 or first > 0:
+                visible = self._visible_ramp(T, L, first, x.device)      # tokens of segment i see first + i slots
+                route_q = x if fold else F.linear(x.float(), route_q_weight)
+                gates, indices = self._route(route_q, archive.route_keys, visible)
         k, q = self._keys_and_queries(x)
         v = _linear(x, self.p, "memory_cell.value_proj")
         hidden, memory = torch.ops.grmx.chunk_scan_segments(k, v, q, memory, self.decay, archive.memories, first, L)
         if side is not main:
-            main.wait_stream(side)       # summaries and new_keys stay referenced until here: their memory is not reused
+            main.wait_stream(side)       # what the side stream allocated stays referenced until the end of this call
         archive.note_pushed(n_seg)
         if archive.storage_dtype != torch.float32:      # the states the scan left in the ring, as the archive stores them
             archive.memories[:, first:first + n_seg] = archive.as_stored(archive.memories[:, first:first + n_seg])
         archive.memories_bf16[:, first:first + n_seg].copy_(archive.memories[:, first:first + n_seg])
-        held = first + n_seg
         routes = []
         if held > 1 or first > 0:
-            visible = self._visible_ramp(T, L, first, x.device)      # tokens of segment i see first + i slots
-            route_q = x if fold else F.linear(x.float(), route_q_weight)
-            gates, indices = self._route(route_q, archive.route_keys, visible)
             ring = archive.memories_bf16[:, :held].reshape(B, held * self.hidden, self.key_dim)
             ln_w = self._fp32_param("aggregator.layer_norm.weight") if self.use_layer_norm else None
             ln_b = self._fp32_param("aggregator.layer_norm.bias") if self.use_layer_norm else None
