@@ -103,10 +103,6 @@ constexpr int kSmemAlloc = kSmemTotal + 1024;
 static_assert(kSmemAlloc <= 232448, "shared memory plan exceeds 227 KiB");
 static_assert(kStageBytes % 1024 == 0 && kStageMb % 1024 == 0 && kStageV % 1024 == 0, "swizzle atoms are 1 KiB");
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
 // 16-byte load through the coherent path (ld.global, never ld.global.nc)
 __device__ __forceinline__ float4 ld_coherent_f4(const float4* ptr) {
   float4 v;
@@ -115,7 +111,6 @@ __device__ __forceinline__ float4 ld_coherent_f4(const float4* ptr) {
 }
 
 // descriptor + byte offset (the start-address field holds addr >> 4 in its low 14 bits)
-__device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
 
 // kSnapshots: also write the state at segment ends (ScanParams::snapshots).  A variant of its own:
 // the test in the state group's loop costs the plain scan a tenth of its speed.

@@ -45,11 +45,6 @@ constexpr int kOffBars = kOffVw + 2 * kTileBytes;
 constexpr int kOffMisc = kOffBars + 16 * 8;
 constexpr int kSmemAlloc = kOffMisc + 32 + 1024;
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
-
 __global__ void __launch_bounds__(kThreads, 1)
 piece_state_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    ScanParams p, SplitInfo split, float* partials, uint32_t* error_word) {

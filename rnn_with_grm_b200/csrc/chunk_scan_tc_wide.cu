@@ -98,10 +98,6 @@ constexpr int kSmemAlloc = 232448;
 static_assert(kSmemTotal + 512 <= kSmemAlloc, "shared memory plan exceeds 227 KiB");
 static_assert(kOffBars % 8 == 0, "barriers are 8-byte aligned");
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
 // k-step kk (16 features) of a K-major [128 x 128] tile held as two sub-tiles
 __device__ __forceinline__ uint32_t kmajor_step(int kk) { return static_cast<uint32_t>((kk >> 2) * kSub + (kk & 3) * 32); }
 

@@ -42,11 +42,6 @@ constexpr int kSmemTotal = kOffMisc + 32;
 constexpr int kSmemAlloc = kSmemTotal + 1024;
 static_assert(kSmemAlloc <= 232448, "shared memory plan exceeds 227 KiB");
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
-
 __global__ void __launch_bounds__(kThreads, 1)
 project_normalize_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          const float* __restrict__ bias, __nv_bfloat16* __restrict__ out_a,

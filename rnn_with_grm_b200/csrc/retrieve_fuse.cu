@@ -484,7 +484,7 @@ retrieve_fuse_rows_kernel(const float* __restrict__ archive, const int64_t* __re
             if (span == K / kSpan - 1 && half == kPieces / 4 - 1) {   // the unit is in registers: its stage can be refilled
               __syncwarp();
               if (lane == 0) {
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_empty[stage])) : "memory");
+                mbar_arrive(&bar_empty[stage]);
               }
             }
             const float* q_cols = s_q + kSpan * span + (kSpan / 4) * kq;
@@ -510,7 +510,7 @@ retrieve_fuse_rows_kernel(const float* __restrict__ archive, const int64_t* __re
         if (c == KC - 1) {   // the unit is in registers: its stage can be refilled
           __syncwarp();
           if (lane == 0) {
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_empty[stage])) : "memory");
+            mbar_arrive(&bar_empty[stage]);
           }
         }
         // kRowsBatch queries at a time (four when no more are left), all of their dot products advancing

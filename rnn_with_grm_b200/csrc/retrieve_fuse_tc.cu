@@ -72,10 +72,6 @@ struct Params {
   int mode;
 };
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
 // The slot mask of a tile is kept as one word per builder warp (each warp writes its own, nobody has to
 // clear anything); readers OR the four.
 __device__ __forceinline__ uint32_t tile_mask(const uint32_t* words) { return words[0] | words[1] | words[2] | words[3]; }

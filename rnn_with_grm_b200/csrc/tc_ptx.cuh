@@ -25,6 +25,10 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -316,6 +320,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   d |= 2ull << 61;
   return d;
 }
+
+// a shared-memory descriptor moved on by `bytes` (start address field, in 16-byte units)
+__device__ __forceinline__ uint64_t desc_add(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
 
 // Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B.
 // bits [4,6) D format (1 = f32); [7,10) A format (1 = bf16); [10,13) B format;
