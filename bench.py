@@ -238,6 +238,28 @@ def time_graph(fn, launches, warmup=3):
     return total / launches
 
 
+def pinned_input_buffer(nbytes, kind):
+    """Page-locked host memory for the input side of the end-to-end leg.  "pinned": torch's pinned allocation.
+    "write-combined": cudaHostAlloc with cudaHostAllocWriteCombined -- the CPU writes it once and never reads
+    it, the GPUs read it over PCIe without snooping the CPU caches."""
+    if kind == "pinned":
+        return torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    import ctypes
+
+    from cuda.bindings import runtime as cudart
+
+    err, ptr = cudart.cudaHostAlloc(nbytes, cudart.cudaHostAllocWriteCombined)
+    if int(err) != 0:
+        raise RuntimeError(f"cudaHostAlloc(write-combined) failed: {err}")
+    raw = (ctypes.c_uint8 * nbytes).from_address(int(ptr))
+    buffer = torch.frombuffer(raw, dtype=torch.uint8)
+    _KEEP_HOST_ALLOCATIONS.append((raw, int(ptr)))               # lives as long as the process
+    return buffer
+
+
+_KEEP_HOST_ALLOCATIONS = []
+
+
 def max_over_ranks(value, device, world):
     if world <= 1:
         return value
@@ -307,7 +329,7 @@ def run_engine(args, rank, world, device, numa):
     parts = [k0, v0, q0, m_in]
     part_bytes = [t.numel() * t.element_size() for t in parts]
     in_bytes = sum(part_bytes)
-    host_in = torch.empty(in_bytes, dtype=torch.uint8).pin_memory()
+    host_in = pinned_input_buffer(in_bytes, args.host_input)
     at = 0
     for t, n in zip(parts, part_bytes):
         host_in[at:at + n].copy_(t.cpu().contiguous().view(torch.uint8).flatten())
@@ -1087,6 +1109,8 @@ def main(argv=None) -> int:
                         help="rows a GPU holds at a time in configuration 5 (296 rows x 2 value blocks = 4 CTAs per SM of a B200)")
     parser.add_argument("--verify-rows", type=int, default=2, help="rows per rank checked against the oracle")
     parser.add_argument("--cpu-budget", type=float, default=10.0, help="seconds of CPU work for cpu_baseline")
+    parser.add_argument("--host-input", choices=["pinned", "write-combined"], default="pinned",
+                        help="how the host buffer of the end-to-end leg's inputs is allocated")
     parser.add_argument("--with-workspace", action="store_true",
                         help="time the two-kernel variant of the cut (piece-state kernel + scan over a caller workspace)")
     parser.add_argument("--only", choices=["full-occupancy", "wide-head", "config4", "segment-retrieval", "layer-retrieval",
