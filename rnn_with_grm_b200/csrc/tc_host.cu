@@ -29,7 +29,6 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// [B, T, D] bf16 tensor, box = 64 features x 128 tokens x 1 row, 128-byte swizzle
 namespace {
 
 // Encoding a tensor map is a driver call of a few microseconds, and a scan needs four of them;
@@ -39,8 +38,7 @@ namespace {
 struct MapKey {
   const void* base;
   int64_t B, T, D;
-  int kind;   // 0: load map (64 x 128 box, 128-byte swizzle), 1: store map (32 x 128 box, 64-byte swizzle),
-              // 2: fp32 matrix rows [B rows, D floats], box = 32 floats x T rows, 128-byte swizzle
+  int kind;   // 0: load map (64 x 128 box, 128-byte swizzle), 1: store map (32 x 128 box, 64-byte swizzle)
   bool operator==(const MapKey& o) const {
     return base == o.base && B == o.B && T == o.T && D == o.D && kind == o.kind;
   }
@@ -63,23 +61,6 @@ bool encode_token_map(CUtensorMap* map, const MapKey& key) {
   }
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;
-  if (key.kind == 2) {
-    const cuuint64_t dims2[2] = {static_cast<cuuint64_t>(key.D), static_cast<cuuint64_t>(key.B)};
-    const cuuint64_t strides2[1] = {static_cast<cuuint64_t>(key.D) * 4};
-    const cuuint32_t box2[2] = {32, static_cast<cuuint32_t>(key.T)};
-    const cuuint32_t elem2[2] = {1, 1};
-    const bool ok2 = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(key.base), dims2, strides2, box2,
-                            elem2, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-    if (ok2) {
-      const int slot = cache.next;
-      cache.keys[slot] = key;
-      cache.maps[slot] = *map;
-      cache.next = (slot + 1) % kMapCacheSlots;
-      if (cache.used < kMapCacheSlots) ++cache.used;
-    }
-    return ok2;
-  }
   const cuuint64_t dims[3] = {static_cast<cuuint64_t>(key.D), static_cast<cuuint64_t>(key.T),
                               static_cast<cuuint64_t>(key.B)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(key.D) * 2, static_cast<cuuint64_t>(key.T) * key.D * 2};
@@ -108,10 +89,6 @@ bool make_token_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, in
 
 bool make_token_half_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, int64_t D) {
   return encode_token_map(map, MapKey{base, B, T, D, 1});
-}
-
-bool make_matrix_rows_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t box_rows) {
-  return encode_token_map(map, MapKey{base, rows, box_rows, K, 2});
 }
 
 namespace {

@@ -381,8 +381,6 @@ EncodeTiledFn encode_tiled_fn();
 bool make_token_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, int64_t D);
 // the same tensor as a store target: box = 32 features x 128 tokens x 1 row, 64-byte swizzle
 bool make_token_half_map(CUtensorMap* map, const void* base, int64_t B, int64_t T, int64_t D);
-// 2-D map over `rows` dense fp32 rows of K floats: box = 32 floats x box_rows rows (at most 256), 128-byte swizzle
-bool make_matrix_rows_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t box_rows);
 bool device_is_sm100();
 // one CTA that lets a bounded wait expire on purpose (see grmx_selftest_bounded_wait)
 int launch_bounded_wait_selftest(uint32_t limit, cudaStream_t stream);
