@@ -103,20 +103,23 @@ constexpr int kFewMaxD = 1024;
 constexpr int64_t kFewManyQueries = 16384;                   // from here on the grid fills every SM several times
 constexpr int kFewPad = 4;                                   // floats between staged query rows: the two halves of a warp read different banks
 
-__host__ __device__ constexpr size_t few_keys_smem_bytes(int D, int queries_per_cta) {
-  return sizeof(float) * ((size_t)D * kFewKeys + (size_t)queries_per_cta * (D + kFewPad));
+__host__ __device__ constexpr size_t few_keys_smem_bytes(int D, int queries_per_cta, int keys = kFewKeys) {
+  return sizeof(float) * ((size_t)D * keys + (size_t)queries_per_cta * (D + kFewPad));
 }
 
-// Selection for the few-keys kernels: lane (half, s) holds the score of key s for the query of its half-warp
-// (two queries per warp at once).  The rank of a key among the visible ones (how many beat it: higher score,
-// or the same score and a lower index) comes from 16 independent shuffles instead of a round of dependent
-// ones per route; the key of rank r is route r.  All 32 lanes must call it together.
+// Selection for the few-keys kernels: kKeys lanes (16: a half-warp, two queries per warp at once; 32: the
+// whole warp) hold the scores of one query, lane s of the group that of key s.  The rank of a key among the
+// visible ones (how many beat it: higher score, or the same score and a lower index) comes from kKeys
+// independent shuffles instead of a round of dependent ones per route; the key of rank r is route r.  All 32
+// lanes must call it together.
+template <int kKeys = kFewKeys>
 __device__ __forceinline__ void few_keys_select(float score, int lane, int64_t b, int64_t q, int64_t Q, int S, bool query_live,
                                                 const int32_t* __restrict__ visible, int top_k, float temperature,
                                                 int64_t* __restrict__ indices_out, float* __restrict__ gates_out,
                                                 float* __restrict__ scores_out) {
-  const int half = lane >> 4;
-  const int s = lane & (kFewKeys - 1);
+  static_assert(kKeys == 16 || kKeys == 32, "a query's scores lie in a half-warp or in a warp");
+  const int group = lane & ~(kKeys - 1);                      // first lane of this query's group
+  const int s = lane & (kKeys - 1);
   if (scores_out != nullptr && query_live && s < S) scores_out[(b * Q + q) * S + s] = score;
   int n_vis = S;
   if (visible != nullptr && query_live) {
@@ -129,23 +132,24 @@ __device__ __forceinline__ void few_keys_select(float score, int lane, int64_t b
       seen ? (((unsigned long long)ordered_bits(score) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)s)) : 0ull;
   int rank = 0;
 #pragma unroll
-  for (int j = 0; j < kFewKeys; ++j) {
-    const unsigned long long other = __shfl_sync(0xffffffffu, mine, (lane & 16) | j);
+  for (int j = 0; j < kKeys; ++j) {
+    const unsigned long long other = __shfl_sync(0xffffffffu, mine, group | j);
     rank += other > mine ? 1 : 0;
   }
   if (R == n_vis) rank = s;                                  // every visible key is taken: identity order
   const bool chosen = seen && rank < R;
-  // softmax over the chosen scores, inside the half-warp
+  // softmax over the chosen scores, inside the group
   const float x = chosen ? score / temperature : -CUDART_INF_F;
   float mx = x;
 #pragma unroll
-  for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  for (int o = kKeys / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   // fmaxf drops NaN; put it back so a NaN score poisons the row as softmax does
-  const unsigned nan_mask = __ballot_sync(0xffffffffu, chosen && x != x) & (half ? 0xffff0000u : 0x0000ffffu);
+  const unsigned group_mask = kKeys == 32 ? 0xffffffffu : (0xffffu << group);
+  const unsigned nan_mask = __ballot_sync(0xffffffffu, chosen && x != x) & group_mask;
   const float e = chosen ? expf(x - mx) : 0.0f;
   float sum = e;
 #pragma unroll
-  for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  for (int o = kKeys / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   if (query_live) {
     int64_t* idx_row = indices_out + (b * Q + q) * top_k;
     float* gate_row = gates_out + (b * Q + q) * top_k;
@@ -153,24 +157,25 @@ __device__ __forceinline__ void few_keys_select(float score, int lane, int64_t b
       idx_row[rank] = s;
       gate_row[rank] = nan_mask != 0u ? CUDART_NAN_F : e / sum;
     }
-    for (int r = R + s; r < top_k; r += kFewKeys) {          // slots without a route
+    for (int r = R + s; r < top_k; r += kKeys) {             // slots without a route
       idx_row[r] = -1;
       gate_row[r] = 0.0f;
     }
   }
 }
 
-// kFewChains queries per half-warp, kFewWarps warps per CTA; TQ: the queries as stored, float or
-// bf16 (widened while they are staged, which is exact: the scores do not depend on it)
-template <int kFewChains, int kFewWarps, typename TQ>
+// kFewChains queries per group of kKeys lanes (a half-warp for up to 16 keys, the warp for up to 32), kFewWarps
+// warps per CTA; TQ: the queries as stored, float or bf16 (widened while they are staged, which is exact: the
+// scores do not depend on it)
+template <int kFewChains, int kFewWarps, typename TQ, int kKeys = kFewKeys>
 __global__ void __launch_bounds__(kFewWarps * 32)
 topk_route_few_keys_kernel(const TQ* __restrict__ queries, const float* __restrict__ keys,
                            const int32_t* __restrict__ visible, int64_t Q, int S, int D, int top_k,
                            float scale, float temperature, int64_t* __restrict__ indices_out,
                            float* __restrict__ gates_out, float* __restrict__ scores_out) {
-  constexpr int kFewPerWarp = 2 * kFewChains;
+  constexpr int kFewPerWarp = (32 / kKeys) * kFewChains;
   constexpr int kFewPerCta = kFewWarps * kFewPerWarp;
-  extern __shared__ float4 s_few[];                           // keys [D/4][kFewKeys], then queries [kFewPerCta][D/4 + 1]
+  extern __shared__ float4 s_few[];                           // keys [D/4][kKeys], then queries [kFewPerCta][D/4 + 1]
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int64_t b = blockIdx.y;
@@ -178,7 +183,7 @@ topk_route_few_keys_kernel(const TQ* __restrict__ queries, const float* __restri
   const int D4 = D >> 2;
   const int row4 = D4 + kFewPad / 4;
   float4* s_keys = s_few;
-  float4* s_q = s_few + (size_t)D4 * kFewKeys + (size_t)warp * kFewPerWarp * row4;   // this warp's queries
+  float4* s_q = s_few + (size_t)D4 * kKeys + (size_t)warp * kFewPerWarp * row4;      // this warp's queries
 
   // this warp's queries are consecutive rows: one contiguous piece of global memory, eight loads per
   // lane in flight; rows past the last query are filled with zeros and dropped below
@@ -230,17 +235,17 @@ topk_route_few_keys_kernel(const TQ* __restrict__ queries, const float* __restri
     }
   }
   const float4* kb = reinterpret_cast<const float4*>(keys + b * (int64_t)S * D);
-  for (int e = threadIdx.x; e < D4 * kFewKeys; e += kFewWarps * 32) {
-    const int s = e & (kFewKeys - 1);
-    const int d4 = e >> 4;
+  for (int e = threadIdx.x; e < D4 * kKeys; e += kFewWarps * 32) {
+    const int s = e & (kKeys - 1);
+    const int d4 = e / kKeys;
     s_keys[e] = s < S ? __ldg(kb + (int64_t)s * D4 + d4) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   }
   __syncthreads();
 
-  const int half = lane >> 4;
-  const int s = lane & (kFewKeys - 1);
+  const int half = lane / kKeys;                              // the group of this lane (always 0 with 32 keys)
+  const int s = lane & (kKeys - 1);
   const float4* ks = s_keys + s;
-  const float4* qs = s_q + (size_t)half * kFewChains * row4;  // chain c of this half: query half * kFewChains + c of the warp
+  const float4* qs = s_q + (size_t)half * kFewChains * row4;  // chain c of this group: query half * kFewChains + c of the warp
   float acc[kFewChains];
 #pragma unroll
   for (int c = 0; c < kFewChains; ++c) acc[c] = 0.0f;
@@ -251,7 +256,7 @@ topk_route_few_keys_kernel(const TQ* __restrict__ queries, const float* __restri
 #pragma unroll
     for (int i = 0; i < kFewDepth; ++i) {
       if (d0 + i < D4) {
-        k4[i] = ks[(d0 + i) * kFewKeys];
+        k4[i] = ks[(d0 + i) * kKeys];
 #pragma unroll
         for (int c = 0; c < kFewChains; ++c) q4[i][c] = qs[c * row4 + d0 + i];
       }
@@ -270,12 +275,13 @@ topk_route_few_keys_kernel(const TQ* __restrict__ queries, const float* __restri
       }
     }
   }
-  // selection in registers, both queries of the warp at once
+  // selection in registers, all groups of the warp at once
 #pragma unroll
   for (int c = 0; c < kFewChains; ++c) {
     const int slot = warp * kFewPerWarp + half * kFewChains + c;
     const int64_t q = q0 + slot;
-    few_keys_select(acc[c] * scale, lane, b, q, Q, S, q < Q, visible, top_k, temperature, indices_out, gates_out, scores_out);
+    few_keys_select<kKeys>(acc[c] * scale, lane, b, q, Q, S, q < Q, visible, top_k, temperature, indices_out, gates_out,
+                           scores_out);
   }
 }
 
@@ -489,12 +495,12 @@ topk_route_kernel(const float* __restrict__ queries, const float* __restrict__ k
 
 namespace grmx {
 namespace {
-template <int kChains, int kWarps, typename TQ>
+template <int kChains, int kWarps, typename TQ, int kKeys = kFewKeys>
 int launch_few_keys(const TQ* queries, const float* keys, const int32_t* visible, int64_t B, int64_t Q, int64_t S,
                     int64_t D, int top_k, float scale, float temperature, int64_t* indices_out, float* gates_out,
                     float* scores_out, cudaStream_t stream) {
-  constexpr int per_cta = 2 * kChains * kWarps;
-  const size_t need = few_keys_smem_bytes(static_cast<int>(D), per_cta);
+  constexpr int per_cta = (32 / kKeys) * kChains * kWarps;
+  const size_t need = few_keys_smem_bytes(static_cast<int>(D), per_cta, kKeys);
   {
     // the opt-in is per device and grows with the largest request seen there
     static std::mutex mutex;
@@ -503,14 +509,14 @@ int launch_few_keys(const TQ* queries, const float* keys, const int32_t* visible
     cudaGetDevice(&device);
     std::lock_guard<std::mutex> lock(mutex);
     if (device < 0 || device >= 64 || need > configured[device]) {
-      const cudaError_t opted = cudaFuncSetAttribute(topk_route_few_keys_kernel<kChains, kWarps, TQ>,
+      const cudaError_t opted = cudaFuncSetAttribute(topk_route_few_keys_kernel<kChains, kWarps, TQ, kKeys>,
                                                      cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(need));
       GRMX_REQUIRE(opted == cudaSuccess, "grmx_topk_route: shared-memory opt-in failed: %s", cudaGetErrorString(opted));
       if (device >= 0 && device < 64) configured[device] = need;
     }
   }
   const dim3 grid(static_cast<unsigned>((Q + per_cta - 1) / per_cta), static_cast<unsigned>(B));
-  topk_route_few_keys_kernel<kChains, kWarps, TQ><<<grid, kWarps * 32, need, stream>>>(
+  topk_route_few_keys_kernel<kChains, kWarps, TQ, kKeys><<<grid, kWarps * 32, need, stream>>>(
       queries, keys, visible, Q, static_cast<int>(S), static_cast<int>(D), top_k, scale, temperature, indices_out,
       gates_out, scores_out);
   return check_launch("topk_route_few_keys");
@@ -582,6 +588,19 @@ extern "C" int grmx_topk_route(const float* queries, const float* keys, const in
     }
     return launch_few_keys<1, 16, float>(queries, keys, visible, B, Q, S, D, top_k, scale, temperature, indices_out, gates_out,
                                   scores_out, static_cast<cudaStream_t>(stream));
+  }
+  // GRMX_ROUTE_WARP_KEYS=off keeps 17..32 keys on the kernel without staging
+  static const bool warp_keys_off = [] {
+    const char* env = getenv("GRMX_ROUTE_WARP_KEYS");
+    return env != nullptr && strcmp(env, "off") == 0;
+  }();
+  if (!warp_keys_off && S > kFewKeys && S <= 32 && Q >= 16 && D >= 4 && D % 4 == 0 && D <= kFewMaxD && aligned &&
+      B <= 65535) {
+    // 17..32 keys (segment-level routing over a full archive): the same staging with the whole warp on one
+    // query, a lane per key; the kernel below reads every key row 16 bytes per lane at a stride of a row, 32
+    // L1 wavefronts per load (measured at 128 rows x 32 queries x 32 keys of 64 features: 20 us)
+    return launch_few_keys<1, 16, float, 32>(queries, keys, visible, B, Q, S, D, top_k, scale, temperature, indices_out,
+                                             gates_out, scores_out, static_cast<cudaStream_t>(stream));
   }
   const size_t smem = (size_t)kWarpsPerCta * S * (sizeof(float) + 1) + 16;
   topk_route_kernel<<<static_cast<unsigned>(blocks), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(

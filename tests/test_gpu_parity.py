@@ -314,11 +314,13 @@ def test_topk_route_bit_exact_against_c_oracle():
 @pytest.mark.parametrize("B,Q,S,D,top_k", [(2, 64, 1, 64, 4), (3, 70, 5, 36, 4), (2, 512, 15, 512, 4), (1, 97, 16, 128, 16),
                                            (2, 130, 9, 4, 2), (1, 64, 16, 1024, 3), (1, 64, 16, 1028, 3), (2, 64, 3, 8, 20), (2, 8200, 15, 64, 4),
                                            (2, 8200, 15, 512, 4), (4, 4100, 16, 128, 8), (1, 16400, 7, 192, 3), (8, 2100, 1, 64, 2),
-                                           (2, 8200, 13, 96, 4)])
+                                           (2, 8200, 13, 96, 4), (128, 32, 32, 64, 4), (3, 16, 17, 8, 4), (2, 41, 31, 128, 8),
+                                           (5, 33, 32, 1024, 32), (2, 300, 20, 36, 20)])
 def test_topk_route_with_few_keys_and_many_queries_bit_exact(B, Q, S, D, top_k):
-    """Per-token routing shapes take the kernels that stage the keys in shared memory (a lane per key; from
-    16384 queries on, with the features in whole tiles of 64, a block of 4 queries x 4 keys per lane); their
-    scores, indices and gates must be those of the C oracle bit for bit, ragged last CTA included."""
+    """Shapes with at most 32 keys take the kernels that stage the keys in shared memory (a lane per key: a
+    half-warp per query up to 16 keys, the warp from 17 to 32; from 16384 queries on, with the features in
+    whole tiles of 64, a block of 4 queries x 4 keys per lane); their scores, indices and gates must be those
+    of the C oracle bit for bit, ragged last CTA included."""
     rng = np.random.default_rng(47 + Q + S)
     qv = rng.standard_normal((B, Q, D)).astype(np.float32)
     kv = rng.standard_normal((B, S, D)).astype(np.float32)
